@@ -61,3 +61,8 @@ class ModelSpec:
     # its tensors live under ``embed_position_name``.
     embed_position: PartSpec | None = None
     embed_position_name: str = "embed_positions."
+    # Additions to the embedded rows (a table row chosen by the token and its predecessor, and the like): pairs
+    # (PartSpec of the embedding-addition registry, tensor-name prefix).  Each may keep per-request state.
+    embed_additions: tuple = ()
+    # Where the checkpoint calls a tensor otherwise than the parts do: the parts' name -> the stored name.
+    stored_names: dict = field(default_factory=dict)

@@ -332,25 +332,84 @@ extern "C" int flint_gather_rows(const void* x, const int* index, void* out, int
 }
 
 // --------------------------------------------------------------------------- expert combine
-// h[t,:] += g[t,0]*y[row_of[t,0],:] + g[t,1]*y[row_of[t,1],:]   (always in this order)
+// h[t,:] += sum_k g[t,k]*y[row_of[t,k],:]   (summed in the order of k, then added)
 __global__ void moe_combine_kernel(float* __restrict__ h, const float* __restrict__ y,
                                    const int* __restrict__ row_of, const float* __restrict__ gates,
-                                   int H) {
+                                   int H, int top) {
   const int t = blockIdx.x;
-  const int r0 = row_of[2 * t], r1 = row_of[2 * t + 1];
-  const float g0 = gates[2 * t], g1 = gates[2 * t + 1];
   for (int d = threadIdx.x; d < H; d += blockDim.x) {
-    float acc = g0 * y[(size_t)r0 * H + d];
-    acc += g1 * y[(size_t)r1 * H + d];
+    float acc = 0.f;
+    for (int k = 0; k < top; ++k)
+      acc = fmaf(gates[(size_t)top * t + k], y[(size_t)row_of[(size_t)top * t + k] * H + d], acc);
     h[(size_t)t * H + d] += acc;
   }
 }
 
 extern "C" int flint_moe_combine(float* h, const float* y, const int* row_of, const float* gates,
-                                 int T, int H, cudaStream_t stream) {
+                                 int T, int H, int top, cudaStream_t stream) {
   if (T <= 0) return 0;
-  moe_combine_kernel<<<T, 256, 0, stream>>>(h, y, row_of, gates, H);
+  if (top < 1) return fail("moe_combine: %d expert rows a token", top);
+  moe_combine_kernel<<<T, 256, 0, stream>>>(h, y, row_of, gates, H, top);
   return check_launch("moe_combine");
+}
+
+// --------------------------------------------------------------------------- hashed pair embedding
+// A table row for the pair (previous token, token), added to the embedded rows: row
+// (prev * mul_prev + cur * mul_cur) mod buckets, and row number `buckets` for a sequence's first token.  The
+// previous token of a portion's first row is the request's state (last[slot]), which the portion's last row
+// renews.  One block: every row's token and previous token are worked out first, then the state is renewed.
+__global__ void __launch_bounds__(1024)
+pair_tokens_kernel(const int* __restrict__ ids, const int* __restrict__ fed_rows, const int* __restrict__ fed_from,
+                   const int* __restrict__ pos, const int* __restrict__ slot, int* __restrict__ last,
+                   int* __restrict__ pair_row, int T, long long mul_prev, long long mul_cur, int buckets) {
+  pdl_launch();
+  pdl_wait();
+  auto token = [&](int r) {
+    const int fed = fed_rows ? fed_rows[r] : -1;
+    return fed >= 0 ? fed_from[fed] : ids[r];
+  };
+  for (int r = threadIdx.x; r < T; r += blockDim.x) {
+    const int cur = token(r);
+    int row = buckets;
+    if (pos[r] > 0) {
+      const bool first = r == 0 || slot[r - 1] != slot[r];       // the first row of its request's portion
+      const long long prev = first ? last[slot[r]] : token(r - 1);
+      row = (int)(((prev * mul_prev + (long long)cur * mul_cur) % buckets + buckets) % buckets);
+    }
+    pair_row[r] = row;
+  }
+  __syncthreads();
+  for (int r = threadIdx.x; r < T; r += blockDim.x)
+    if (r == T - 1 || slot[r + 1] != slot[r]) last[slot[r]] = token(r);
+}
+
+template <typename TT>
+__global__ void add_rows_kernel(const int* __restrict__ rows, const TT* __restrict__ table, float* __restrict__ out,
+                                int H) {
+  pdl_launch();
+  pdl_wait();
+  const int r = blockIdx.x;
+  const TT* src = table + (size_t)rows[r] * H;
+  float* dst = out + (size_t)r * H;
+  for (int d = threadIdx.x; d < H; d += blockDim.x) dst[d] += to_f32(src[d]);
+}
+
+// out [T, H] += table[pair row]; table [buckets + 1, H]; last [slots] int32; pair_row [T] scratch.
+extern "C" int flint_pair_embed_add(const int* ids, const int* fed_rows, const int* fed_from, const int* pos,
+                                    const int* slot, int* last, int* pair_row, const void* table, int table_dtype,
+                                    float* out, int T, int H, long long mul_prev, long long mul_cur, int buckets,
+                                    cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (H <= 0 || buckets <= 0) return fail("pair_embed: bad sizes H=%d buckets=%d", H, buckets);
+  if ((fed_rows == nullptr) != (fed_from == nullptr)) return fail("pair_embed: fed rows and their source come together");
+  launch_pdl(pair_tokens_kernel, dim3(1), dim3(T >= 1024 ? 1024 : ((T + 31) / 32) * 32), 0, stream, ids, fed_rows,
+             fed_from, pos, slot, last, pair_row, T, mul_prev, mul_cur, buckets);
+  int rc = check_launch("pair_embed (tokens)");
+  if (rc) return rc;
+  const int threads = H >= 1024 ? 256 : (H >= 256 ? 128 : 64);
+  FLINT_DISPATCH_DTYPE(table_dtype, TT,
+      launch_pdl(add_rows_kernel<TT>, dim3(T), dim3(threads), 0, stream, (const int*)pair_row, (const TT*)table, out, H));
+  return check_launch("pair_embed (rows)");
 }
 
 // x[r, c] += sum_z partials[z][r, c] (+ bias[c]): the fallback for widths the fused row kernel refuses.

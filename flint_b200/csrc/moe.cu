@@ -1,5 +1,5 @@
-// Routing for a top-2 mixture of experts: router logits and sparsemixer selection, and
-// the plan that sorts token rows by expert for the grouped products.
+// Routing for a mixture of experts: router logits with sparsemixer top-2 selection or a softmax choice of the
+// top k limited to groups, and the plan that sorts token rows by expert for the grouped products.
 //
 // The reference has no mixture of experts (its feed-forward is dense:
 // crates/thuban_model/src/ops/mlp.rs:24-79); these kernels have no counterpart there.
@@ -40,17 +40,11 @@ __device__ __forceinline__ void load_vec(const __nv_bfloat16* p, float* f) {
   }
 }
 
+// The float32 router logits of the block's TT tokens into s_all [TT, E] (shared memory; xs holds the staged rows).
 template <typename TW>
-__global__ void __launch_bounds__(ROUTER_WARPS * 32)
-router_sparsemixer_kernel(const float* __restrict__ x, const TW* __restrict__ wr, float eps,
-                          int* __restrict__ expert_ids, float* __restrict__ gates,
-                          float* __restrict__ logits_out, int T, int H, int E, int vec_ok) {
-  extern __shared__ float smem[];   // TT rows of x, then TT x E logits
-  float* xs = smem;
-  float* s_all = smem + (size_t)TT * H;
+__device__ __forceinline__ void block_router_logits(const float* __restrict__ x, const TW* __restrict__ wr, float* xs,
+                                                    float* s_all, int t0, int nt, int H, int E, int vec_ok) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int t0 = blockIdx.x * TT;
-  const int nt = min(TT, T - t0);
   if (vec_ok) {        // rows are staged with 16-byte loads, several in flight per thread
     const int n4 = TT * H / 4, live4 = nt * H / 4;
     const float4* src = reinterpret_cast<const float4*>(x + (size_t)t0 * H);
@@ -96,6 +90,19 @@ router_sparsemixer_kernel(const float* __restrict__ x, const TW* __restrict__ wr
     }
   }
   __syncthreads();
+}
+
+template <typename TW>
+__global__ void __launch_bounds__(ROUTER_WARPS * 32)
+router_sparsemixer_kernel(const float* __restrict__ x, const TW* __restrict__ wr, float eps,
+                          int* __restrict__ expert_ids, float* __restrict__ gates,
+                          float* __restrict__ logits_out, int T, int H, int E, int vec_ok) {
+  extern __shared__ float smem[];   // TT rows of x, then TT x E logits
+  float* xs = smem;
+  float* s_all = smem + (size_t)TT * H;
+  const int t0 = blockIdx.x * TT;
+  const int nt = min(TT, T - t0);
+  block_router_logits<TW>(x, wr, xs, s_all, t0, nt, H, E, vec_ok);
   if (threadIdx.x >= nt) return;
   const int t = t0 + threadIdx.x;
   const float* s = s_all + threadIdx.x * E;
@@ -126,13 +133,78 @@ router_sparsemixer_kernel(const float* __restrict__ x, const TW* __restrict__ wr
   gates[2 * t + 1] = gate[1];
 }
 
-// One block.  expert_ids [T*2] -> per-expert counts, offsets (exclusive scan), the sorted row
+// Softmax router with a choice limited to groups: s = softmax(logits); the experts form n_groups equal groups of
+// neighbours, a group scores as its best member, only members of the `keep` best groups may be chosen, and the
+// `top` best of those are (lowest index first among equals).  Gates: s_e / (sum of the chosen s + 1e-20) * scale.
+// One thread per token does the selection; everything is float32.
+constexpr int MAX_TOP = 16;
+template <typename TW>
+__global__ void __launch_bounds__(ROUTER_WARPS * 32)
+router_topk_kernel(const float* __restrict__ x, const TW* __restrict__ wr, int top, int n_groups, int keep,
+                   float out_scale, int* __restrict__ expert_ids, float* __restrict__ gates,
+                   float* __restrict__ logits_out, int T, int H, int E, int vec_ok) {
+  extern __shared__ float smem[];   // TT rows of x, then TT x E logits (turned into scores in place)
+  float* xs = smem;
+  float* s_all = smem + (size_t)TT * H;
+  pdl_launch();
+  pdl_wait();
+  const int t0 = blockIdx.x * TT;
+  const int nt = min(TT, T - t0);
+  block_router_logits<TW>(x, wr, xs, s_all, t0, nt, H, E, vec_ok);
+  if (threadIdx.x >= nt) return;
+  const int t = t0 + threadIdx.x;
+  float* s = s_all + threadIdx.x * E;
+  if (logits_out)
+    for (int e = 0; e < E; ++e) logits_out[(size_t)t * E + e] = s[e];
+  float m = -INFINITY;
+  for (int e = 0; e < E; ++e) m = fmaxf(m, s[e]);
+  float denom = 0.f;
+  for (int e = 0; e < E; ++e) denom += expf(s[e] - m);
+  for (int e = 0; e < E; ++e) s[e] = expf(s[e] - m) / denom;
+  // the groups that stay: bit g of `kept`
+  const int per = E / n_groups;
+  unsigned long long kept = 0ull;
+  if (keep >= n_groups) kept = ~0ull;
+  else
+    for (int r = 0; r < keep; ++r) {
+      float best = -1.f;
+      int bg = 0;
+      for (int g = 0; g < n_groups; ++g) {
+        if (kept >> g & 1ull) continue;
+        float gs = 0.f;
+        for (int e = g * per; e < (g + 1) * per; ++e) gs = fmaxf(gs, s[e]);
+        if (gs > best) { best = gs; bg = g; }
+      }
+      kept |= 1ull << bg;
+    }
+  int sel[MAX_TOP];
+  float val[MAX_TOP], sum = 0.f;
+  for (int r = 0; r < top; ++r) {
+    float best = -1.f;
+    int be = 0;
+    for (int e = 0; e < E; ++e) {
+      if (!(kept >> (e / per) & 1ull)) continue;
+      bool taken = false;
+      for (int q = 0; q < r; ++q) taken |= sel[q] == e;
+      if (!taken && s[e] > best) { best = s[e]; be = e; }
+    }
+    sel[r] = be;
+    val[r] = best;
+    sum += best;
+  }
+  for (int r = 0; r < top; ++r) {
+    expert_ids[(size_t)t * top + r] = sel[r];
+    gates[(size_t)t * top + r] = val[r] / (sum + 1e-20f) * out_scale;
+  }
+}
+
+// One block.  expert_ids [T*top] -> per-expert counts, offsets (exclusive scan), the sorted row
 // of every (token, choice) and the tile map for the grouped products.
 __global__ void moe_plan_kernel(const int* __restrict__ expert_ids, int n_assign, int E,
                                 int tile_rows, int* __restrict__ counts, int* __restrict__ offsets,
                                 int* __restrict__ row_of, int* __restrict__ token_of,
                                 int* __restrict__ tile_expert, int* __restrict__ tile_row0,
-                                int* __restrict__ n_tiles, int max_tiles) {
+                                int* __restrict__ n_tiles, int max_tiles, int top) {
   __shared__ int cnt[MAX_E];
   __shared__ int off[MAX_E + 1];
   pdl_launch();
@@ -166,7 +238,7 @@ __global__ void moe_plan_kernel(const int* __restrict__ expert_ids, int n_assign
   for (int a = threadIdx.x; a < n_assign; a += blockDim.x) {
     const int row = off[expert_ids[a]] + row_of[a];
     row_of[a] = row;
-    token_of[row] = a >> 1;
+    token_of[row] = a / top;
   }
 }
 
@@ -179,7 +251,7 @@ moe_dispatch_kernel(const int* __restrict__ expert_ids, int n_assign, int E, int
                     int* __restrict__ counts, int* __restrict__ offsets, int* __restrict__ row_of,
                     int* __restrict__ token_of, int* __restrict__ tile_expert, int* __restrict__ tile_row0,
                     int* __restrict__ n_tiles, int max_tiles, const uint4* __restrict__ x,
-                    uint4* __restrict__ xs, int row_vecs) {
+                    uint4* __restrict__ xs, int row_vecs, int top) {
   __shared__ int ids[DISPATCH_MAX];
   __shared__ int cnt[MAX_E];
   __shared__ int off[MAX_E + 1];
@@ -227,9 +299,9 @@ moe_dispatch_kernel(const int* __restrict__ expert_ids, int n_assign, int E, int
     const int row = off[ids[tid]] + rank;
     if (blockIdx.x == 0) {
       row_of[tid] = row;
-      token_of[row] = tid >> 1;
+      token_of[row] = tid / top;
     }
-    if (row == (int)blockIdx.x) my_token = tid >> 1;
+    if (row == (int)blockIdx.x) my_token = tid / top;
   }
   __syncthreads();
   const uint4* src = x + (size_t)my_token * row_vecs;
@@ -262,6 +334,34 @@ extern "C" int flint_router_sparsemixer(const float* x, const void* wr, int w_dt
   return check_launch("router_sparsemixer");
 }
 
+// x [T, H] float32, wr [E, H]; expert_ids and gates [T, top].
+extern "C" int flint_router_topk(const float* x, const void* wr, int w_dtype, int top, int n_groups, int keep,
+                                 float out_scale, int* expert_ids, float* gates, float* logits_out, int T, int H, int E,
+                                 cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (E < 1 || E > MAX_E) return fail("router: %d experts (supported: 1..%d)", E, MAX_E);
+  if (top < 1 || top > MAX_TOP || top > E) return fail("router: %d choices of %d experts (supported: 1..%d)", top, E, MAX_TOP);
+  if (n_groups < 1 || n_groups > 64 || E % n_groups) return fail("router: %d experts do not form %d equal groups (up to 64)", E, n_groups);
+  if (keep < 1 || keep > n_groups) return fail("router: %d of %d groups kept", keep, n_groups);
+  if (keep * (E / n_groups) < top) return fail("router: %d kept groups of %d experts cannot give %d choices", keep, E / n_groups, top);
+  const size_t smem = ((size_t)TT * H + (size_t)TT * E) * sizeof(float);
+  if (smem > 200 * 1024) return fail("router: width %d is too large for the staging buffer", H);
+  const int blocks = (T + TT - 1) / TT;
+  const int vec_ok = (H % 8 == 0) && (((uintptr_t)wr & 15) == 0) && (((uintptr_t)x & 15) == 0);
+  static bool configured[2] = {false, false};
+  if (smem > 48 * 1024 && !configured[w_dtype ? 1 : 0]) {
+    cudaError_t e = w_dtype == FLINT_F32
+        ? cudaFuncSetAttribute(router_topk_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)
+        : cudaFuncSetAttribute(router_topk_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    if (e != cudaSuccess) return fail("router: cannot raise shared memory: %s", cudaGetErrorString(e));
+    configured[w_dtype ? 1 : 0] = true;
+  }
+  FLINT_DISPATCH_DTYPE(w_dtype, TW,
+      (launch_pdl(router_topk_kernel<TW>, dim3(blocks), dim3(ROUTER_WARPS * 32), smem, stream, x, (const TW*)wr, top,
+                  n_groups, keep, out_scale, expert_ids, gates, logits_out, T, H, E, vec_ok)));
+  return check_launch("router_topk");
+}
+
 // Upper bound of row tiles for n_assign rows over E experts.
 extern "C" int flint_moe_max_tiles(int n_assign, int E, int tile_rows) {
   return n_assign / tile_rows + (E < n_assign ? E : n_assign);
@@ -269,14 +369,15 @@ extern "C" int flint_moe_max_tiles(int n_assign, int E, int tile_rows) {
 
 extern "C" int flint_moe_plan(const int* expert_ids, int n_assign, int E, int tile_rows, int* counts,
                               int* offsets, int* row_of, int* token_of, int* tile_expert,
-                              int* tile_row0, int* n_tiles, int max_tiles, cudaStream_t stream) {
+                              int* tile_row0, int* n_tiles, int max_tiles, int top, cudaStream_t stream) {
   if (n_assign <= 0) return 0;
+  if (top < 1) return fail("moe_plan: %d choices a token", top);
   if (E < 1 || E > MAX_E) return fail("moe_plan: %d experts (supported: 1..%d)", E, MAX_E);
   if (tile_rows <= 0) return fail("moe_plan: bad tile size %d", tile_rows);
   if (max_tiles < flint_moe_max_tiles(n_assign, E, tile_rows))
     return fail("moe_plan: tile map of %d entries is too small", max_tiles);
   launch_pdl(moe_plan_kernel, dim3(1), dim3(1024), 0, stream, expert_ids, n_assign, E, tile_rows, counts, offsets, row_of,
-                                          token_of, tile_expert, tile_row0, n_tiles, max_tiles);
+                                          token_of, tile_expert, tile_row0, n_tiles, max_tiles, top);
   return check_launch("moe_plan");
 }
 
@@ -284,9 +385,10 @@ extern "C" int flint_moe_plan(const int* expert_ids, int n_assign, int E, int ti
 // of a multiple of 16 bytes (x and xs 16-byte aligned).
 extern "C" int flint_moe_dispatch(const int* expert_ids, int n_assign, int E, int tile_rows, int* counts,
                                   int* offsets, int* row_of, int* token_of, int* tile_expert, int* tile_row0,
-                                  int* n_tiles, int max_tiles, const void* x, void* xs, int row_bytes,
+                                  int* n_tiles, int max_tiles, const void* x, void* xs, int row_bytes, int top,
                                   cudaStream_t stream) {
   if (n_assign <= 0) return 0;
+  if (top < 1) return fail("moe_dispatch: %d choices a token", top);
   if (n_assign > DISPATCH_MAX) return fail("moe_dispatch: %d assignments (up to %d)", n_assign, DISPATCH_MAX);
   if (E < 1 || E > MAX_E) return fail("moe_dispatch: %d experts (supported: 1..%d)", E, MAX_E);
   if (tile_rows <= 0) return fail("moe_dispatch: bad tile size %d", tile_rows);
@@ -296,7 +398,7 @@ extern "C" int flint_moe_dispatch(const int* expert_ids, int n_assign, int E, in
     return fail("moe_dispatch: rows must be a multiple of 16 bytes and 16-byte aligned");
   launch_pdl(moe_dispatch_kernel, dim3(n_assign), dim3(256), 0, stream, expert_ids, n_assign, E, tile_rows, counts,
              offsets, row_of, token_of, tile_expert, tile_row0, n_tiles, max_tiles, (const uint4*)x, (uint4*)xs,
-             row_bytes / 16);
+             row_bytes / 16, top);
   return check_launch("moe_dispatch");
 }
 

@@ -60,11 +60,12 @@ class MoePlan:
     max_tiles: int
     counts: torch.Tensor       # [E]
     offsets: torch.Tensor      # [E+1]
-    row_of: torch.Tensor       # [T, 2] sorted row of (token, choice)
-    token_of: torch.Tensor     # [2T] token of each sorted row
+    row_of: torch.Tensor       # [T, top] sorted row of (token, choice)
+    token_of: torch.Tensor     # [top T] token of each sorted row
     tile_expert: torch.Tensor  # [max_tiles]
     tile_row0: torch.Tensor    # [max_tiles]
     n_tiles: torch.Tensor      # [1]
+    top: int = 2               # choices per token
 
 
 class CudaOps:
@@ -234,7 +235,7 @@ class CudaOps:
         if gamma is not None and (gamma.dtype != torch.float32 or gamma.numel() != H):
             raise KernelError("row_norm: scale must be float32 of the row width")
         partials = bias = y = row_of = gts = None
-        S, stride = 0, 0
+        S, stride, top = 0, 0, 0
         if pending is not None:
             if pending.partials is not None:
                 partials = pending.partials
@@ -245,7 +246,8 @@ class CudaOps:
             if pending.y is not None:
                 y, row_of, gts = pending.y, pending.row_of, pending.gates
                 _check(y, "pending expert rows", torch.float32, 2)
-                if y.shape[1] != H or row_of.numel() != 2 * T or gts.numel() != 2 * T:
+                top = row_of.numel() // max(T, 1)
+                if y.shape[1] != H or top < 1 or row_of.numel() != top * T or gts.numel() != top * T:
                     raise KernelError("row_norm: pending expert rows do not match the residual")
         wr = logits = None
         E, jit, ids, gates = 0, 0.0, None, None
@@ -260,7 +262,7 @@ class CudaOps:
             if wr.shape[1] != H or ids.numel() != 2 * T or gates.numel() != 2 * T:
                 raise KernelError("row_norm: router shapes do not match")
         self._run("row_fused", "flint_row_norm", _ptr(x), _ptr(row_index), c_int(rows), c_int(H), _ptr(partials),
-                  c_int(S), c_longlong(stride), _ptr(bias), _ptr(y), _ptr(row_of), _ptr(gts), _ptr(gamma), _ptr(beta),
+                  c_int(S), c_longlong(stride), _ptr(bias), _ptr(y), _ptr(row_of), _ptr(gts), c_int(top), _ptr(gamma), _ptr(beta),
                   c_float(eps), c_int({"layer": 0, "rms": 1}[mode]), _ptr(out_f32), _ptr(out_bf16), _ptr(wr),
                   c_int(_code(wr.dtype) if wr is not None else 0), c_int(E), c_float(jit), _ptr(ids), _ptr(gates),
                   _ptr(logits))
@@ -328,9 +330,11 @@ class CudaOps:
         _check(h, "h", torch.float32, 2)
         _check(y, "y", torch.float32, 2)
         T, H = h.shape
-        if y.shape[1] != H or row_of.numel() != 2 * T or gates.numel() != 2 * T:
+        top = row_of.numel() // max(T, 1)
+        if y.shape[1] != H or top < 1 or row_of.numel() != top * T or gates.numel() != top * T:
             raise KernelError("moe_combine: shapes do not match")
-        self._run("elementwise", "flint_moe_combine", _ptr(h), _ptr(y), _ptr(row_of), _ptr(gates), c_int(T), c_int(H))
+        self._run("elementwise", "flint_moe_combine", _ptr(h), _ptr(y), _ptr(row_of), _ptr(gates), c_int(T), c_int(H),
+                  c_int(top))
 
     # ------------------------------------------------------------------ matrix products
     def gemm(self, x, w, out, bias=None, accumulate=False):
@@ -474,11 +478,11 @@ class CudaOps:
                 return bn
         return 256
 
-    def moe_tile_rows(self, n_tokens, n_experts, weight_dtype):
-        """Row-tile size the plan should use for grouped products over these weights."""
+    def moe_tile_rows(self, n_tokens, n_experts, weight_dtype, top=2):
+        """Row-tile size the plan should use for grouped products over these weights (``top`` choices a token)."""
         if weight_dtype != torch.bfloat16:
             return 64
-        return self.token_tile(-(-2 * n_tokens // n_experts))
+        return self.token_tile(-(-top * n_tokens // n_experts))
 
     def _gemm_tc(self, x, w, gated, out, bias, accumulate, act_code, plan, M, N, K, plan_ready=False):
         if plan is not None:
@@ -694,6 +698,110 @@ class CudaOps:
                   c_int(nq), c_int(nkv), c_int(hd), c_int(window), c_float(scale), c_int(split_keys), c_int(n_splits),
                   _ptr(scratch), _ptr(rows))
 
+    # ------------------------------------------------------------------ attention over a cached latent
+    def head_products(self, x, w, out):
+        """A small product per head: out[t, h, :] = w[h] @ x[t, h, :].  x [T, H, K], w [H, N, K], out [T, H, N]; x and
+        out may be views into wider rows (their last axis contiguous)."""
+        _check(x, "x", dims=3, contiguous=False)
+        _check(out, "out", dims=3, contiguous=False)
+        _check(w, "w", dims=3)
+        T, H, K = x.shape
+        N = w.shape[1]
+        if w.shape[0] != H or w.shape[2] != K or tuple(out.shape) != (T, H, N):
+            raise KernelError(f"head_products: shapes x{tuple(x.shape)} w{tuple(w.shape)} out{tuple(out.shape)} do not match")
+        if x.stride(2) != 1 or out.stride(2) != 1:
+            raise KernelError("head_products: the last axis must be contiguous")
+        for h in range(H):
+            self.gemm(x[:, h, :], w[h], out[:, h, :])
+
+    def latent_prepare(self, proj, pos, slot, cos, sin, rot_dims, style, norm_w, eps, q_plain, qa, cache, H, D, R, C,
+                       write_kv, status):
+        """proj [S, T, W] float32 (partial sums of [q | latent] projections, W = H (D + R) + (C + R if
+        ``write_kv``)): the plain q dims go to q_plain [T, H, D], the rotated q dims into the last R numbers of
+        qa [T, H, C + R], and, with ``write_kv``, the token's cache row [normed latent | rotated key part | 0...]
+        into its page.  ``rot_dims`` of the R dims rotate, in ``style`` ("interleaved": 2i with 2i + 1;
+        "half": i with i + rot_dims/2)."""
+        if style not in ("half", "interleaved"):
+            raise KernelError(f"latent_prepare: unknown rotation style {style!r}")
+        if proj.dim() == 2:
+            proj = proj.unsqueeze(0)
+        _check(proj, "proj", torch.float32, 3)
+        S, T, W = proj.shape
+        if W != H * (D + R) + ((C + R) if write_kv else 0):
+            raise KernelError("latent_prepare: the projection's width does not match the sizes")
+        _check(q_plain, "q_plain", qa.dtype, 3)
+        _check(qa, "qa", dims=3)
+        if tuple(q_plain.shape) != (T, H, D) or tuple(qa.shape) != (T, H, C + R):
+            raise KernelError("latent_prepare: q buffers do not match the sizes")
+        _check(cos, "cos", torch.float32, 2)
+        _check(sin, "sin", torch.float32, 2)
+        if rot_dims and cos.shape[1] * 2 != rot_dims:
+            raise KernelError("latent_prepare: table width must be rot_dims/2")
+        k = bt = None
+        cdt, P, max_pages, row_w = F32, 16, 0, 0
+        if write_kv:
+            k, bt, P = cache.k, cache.block_table, cache.page_size
+            cdt, max_pages, row_w = _code(k.dtype), bt.shape[1], k.shape[-1]
+            if tuple(k.shape[1:]) != (1, P, row_w) or row_w < C + R or row_w % 8:
+                raise KernelError(f"latent_prepare: cache pages are {tuple(k.shape[1:])}, expected (1, {P}, >= {C + R})")
+            if norm_w is None or norm_w.dtype != torch.float32 or norm_w.numel() != C:
+                raise KernelError("latent_prepare: the latent's norm scale must be float32 of the latent size")
+        self._run("latent", "flint_latent_prepare", _ptr(proj), c_int(S), c_longlong(proj.stride(0)), _ptr(pos), _ptr(slot),
+                  _ptr(cos), _ptr(sin), c_int(rot_dims), c_int(1 if style == "interleaved" else 0), _ptr(norm_w),
+                  c_float(eps), _ptr(q_plain), _ptr(qa), c_int(_code(qa.dtype)), _ptr(k), c_int(cdt), _ptr(bt),
+                  c_int(max_pages), c_int(P), c_int(T), c_int(H), c_int(D), c_int(R), c_int(C), c_int(row_w),
+                  c_int(1 if write_kv else 0), _ptr(status))
+
+    def latent_attention_plan(self, T, H, span):
+        """(keys per split, splits) for the float32-pipe kernel: enough warps to fill the device, at least 64
+        keys each."""
+        base = T * -(-H // 4)
+        n = max(1, min(-(-max(span, 1) // 64), -(-8 * self.sm_count // base)))
+        keys = -(-(-(-max(span, 1) // n)) // 32) * 32
+        return keys, -(-max(span, 1) // keys)
+
+    def latent_attention(self, qa, cache, step, out, H, C, window, scale, splits=None, rows=None):
+        """Every row's heads over its request's cached latent rows: qa [T, H, Dk] (key up-projection folded in)
+        -> out [T, H, C], the probability-weighted sum of the latents (causal, ``window`` 0 = all keys)."""
+        _check(qa, "qa", dims=3)
+        _check(out, "out", qa.dtype, 3)
+        T, Dk = qa.shape[0], qa.shape[2]
+        k, P = cache.k, cache.page_size
+        row_w = k.shape[-1]
+        if qa.shape[1] != H or tuple(out.shape) != (T, H, C) or tuple(k.shape[1:]) != (1, P, row_w) or row_w < Dk:
+            raise KernelError("latent_attention: shapes do not match")
+        if rows is not None:
+            _check(rows, "rows", torch.int32, 1)
+            T = rows.numel()
+        span = min(step.max_kv_len, window) if window else step.max_kv_len
+        keys, n = splits if splits is not None else self.latent_attention_plan(T, H, span)
+        if keys * n < span:
+            raise KernelError(f"latent_attention: {n} splits of {keys} keys do not cover {span} keys")
+        scratch = torch.empty(T * H * n * (C + 2), dtype=torch.float32, device=qa.device) if n > 1 else None
+        self._run("latent", "flint_latent_attention", _ptr(qa), c_int(_code(qa.dtype)), _ptr(k), c_int(_code(k.dtype)),
+                  _ptr(cache.block_table), c_int(cache.block_table.shape[1]), c_int(P), _ptr(step.pos), _ptr(step.slot),
+                  _ptr(out), c_int(T), c_int(H), c_int(C), c_int(Dk), c_int(row_w), c_int(window), c_float(scale),
+                  c_int(keys), c_int(n), _ptr(scratch), _ptr(rows))
+
+    # ------------------------------------------------------------------ additions to the embedded rows
+    def pair_embed_add(self, ids, pos, slot, last, table, out, mul_prev, mul_cur, fed_rows=None, fed_from=None):
+        """out [T, H] += table[row of the pair (previous token, token)]: row (prev * mul_prev + cur * mul_cur) mod
+        buckets, table [buckets + 1, H] with the last row for a sequence's first token.  ``last`` [slots] int32
+        holds each request's newest token between steps and is renewed here."""
+        _check(ids, "ids", torch.int32, 1)
+        _check(last, "last", torch.int32, 1)
+        _check(table, "table", dims=2)
+        _check(out, "out", torch.float32, 2)
+        T, H = out.shape
+        if ids.numel() != T or table.shape[1] != H or table.shape[0] < 2:
+            raise KernelError("pair_embed_add: shapes do not match")
+        if (fed_rows is None) != (fed_from is None):
+            raise KernelError("pair_embed_add: fed rows and their source come together")
+        pair_row = torch.empty(T, dtype=torch.int32, device=out.device)
+        self._run("elementwise", "flint_pair_embed_add", _ptr(ids), _ptr(fed_rows), _ptr(fed_from), _ptr(pos), _ptr(slot),
+                  _ptr(last), _ptr(pair_row), _ptr(table), c_int(_code(table.dtype)), _ptr(out), c_int(T), c_int(H),
+                  c_longlong(int(mul_prev)), c_longlong(int(mul_cur)), c_int(table.shape[0] - 1))
+
     # ------------------------------------------------------------------ routing
     def router_sparsemixer(self, x, wr, eps, expert_ids, gates, logits_out=None):
         _check(x, "x", torch.float32, 2)
@@ -707,9 +815,29 @@ class CudaOps:
         self._run("moe", "flint_router_sparsemixer", _ptr(x), _ptr(wr), c_int(_code(wr.dtype)), c_float(eps),
                   _ptr(expert_ids), _ptr(gates), _ptr(logits_out), c_int(T), c_int(H), c_int(E))
 
+    def router_topk(self, x, wr, top, n_groups, keep, scale, expert_ids, gates, logits_out=None):
+        """Softmax router whose choice is limited to groups: scores softmax(x @ wr.T) in float32; the experts form
+        ``n_groups`` equal groups of neighbours, a group scores as its best member, the ``top`` best experts of
+        the ``keep`` best groups are chosen; gates are the chosen scores over their sum, times ``scale``.
+        expert_ids and gates [T, top]."""
+        _check(x, "x", torch.float32, 2)
+        _check(wr, "router weight", dims=2)
+        T, H = x.shape
+        E = wr.shape[0]
+        if wr.shape[1] != H:
+            raise KernelError("router: weight width does not match")
+        _check(expert_ids, "expert_ids", torch.int32, 2)
+        _check(gates, "gates", torch.float32, 2)
+        if tuple(expert_ids.shape) != (T, top) or tuple(gates.shape) != (T, top):
+            raise KernelError(f"router: choices and gates must be [{T}, {top}]")
+        if logits_out is not None:
+            _check(logits_out, "router logits", torch.float32, 2)
+        self._run("moe", "flint_router_topk", _ptr(x), _ptr(wr), c_int(_code(wr.dtype)), c_int(top), c_int(n_groups),
+                  c_int(keep), c_float(scale), _ptr(expert_ids), _ptr(gates), _ptr(logits_out), c_int(T), c_int(H), c_int(E))
+
     def _plan_buffers(self, expert_ids, n_experts, tile_rows):
-        _check(expert_ids, "expert_ids", torch.int32)
-        n = expert_ids.numel()
+        _check(expert_ids, "expert_ids", torch.int32, 2)
+        n, top = expert_ids.numel(), expert_ids.shape[1]
         dev = expert_ids.device
         max_tiles = n // tile_rows + min(n_experts, n)
         ints = torch.empty(n_experts + (n_experts + 1) + n + n + 2 * max_tiles + 1, dtype=torch.int32, device=dev)
@@ -719,14 +847,14 @@ class CudaOps:
             parts.append(ints[o:o + size])
             o += size
         counts, offsets, row_of, token_of, tile_expert, tile_row0, n_tiles = parts
-        plan = MoePlan(n_experts, tile_rows, max_tiles, counts, offsets, row_of.view(-1, 2), token_of,
-                       tile_expert, tile_row0, n_tiles)
+        plan = MoePlan(n_experts, tile_rows, max_tiles, counts, offsets, row_of.view(-1, top), token_of,
+                       tile_expert, tile_row0, n_tiles, top)
         return plan, [_ptr(t) for t in parts]
 
     def moe_plan(self, expert_ids, n_experts, tile_rows) -> MoePlan:
         plan, ptrs = self._plan_buffers(expert_ids, n_experts, tile_rows)
         self._run("moe", "flint_moe_plan", _ptr(expert_ids), c_int(expert_ids.numel()), c_int(n_experts),
-                  c_int(tile_rows), *ptrs, c_int(plan.max_tiles))
+                  c_int(tile_rows), *ptrs, c_int(plan.max_tiles), c_int(plan.top))
         return plan
 
     def moe_dispatch(self, expert_ids, n_experts, tile_rows, x):
@@ -742,7 +870,7 @@ class CudaOps:
             return plan, xs
         plan, ptrs = self._plan_buffers(expert_ids, n_experts, tile_rows)
         self._run("moe", "flint_moe_dispatch", _ptr(expert_ids), c_int(n), c_int(n_experts), c_int(tile_rows), *ptrs,
-                  c_int(plan.max_tiles), _ptr(x), _ptr(xs), c_int(row_bytes))
+                  c_int(plan.max_tiles), _ptr(x), _ptr(xs), c_int(row_bytes), c_int(plan.top))
         return plan, xs
 
     # ------------------------------------------------------------------ sampling

@@ -26,7 +26,7 @@ struct RowArgs {
   float* x;
   const int* row_index;
   const float* partials; int n_partials; long long partial_stride; const float* add_bias;
-  const float* comb_y; const int* comb_row_of; const float* comb_gates;
+  const float* comb_y; const int* comb_row_of; const float* comb_gates; int comb_top;
   const float* gamma; const float* beta; float eps; int mode;
   float* out_f32; __nv_bfloat16* out_bf16;
   const void* wr; int E; float jitter_eps; int* expert_ids; float* gates;
@@ -149,20 +149,22 @@ row_norm_kernel(const __grid_constant__ RowArgs a) {
       }
     }
     if (a.comb_y) {
-      const int r0 = a.comb_row_of[2 * src], r1 = a.comb_row_of[2 * src + 1];
-      const float g0 = a.comb_gates[2 * src], g1 = a.comb_gates[2 * src + 1];
-      const float* y0 = a.comb_y + (size_t)r0 * H;
-      const float* y1 = a.comb_y + (size_t)r1 * H;
+      // the chosen experts' rows times their gates, summed in the order of the choices, then added: the order
+      // of moe_combine
+      float4 t[VPT];
 #pragma unroll
-      for (int i = 0; i < VPT; ++i) {
-        const int c = threadIdx.x + i * blockDim.x;
-        if (c < n4) {
-          float4 t = make_float4(0.f, 0.f, 0.f, 0.f);   // g0*y0 + g1*y1 first, then added: the order of moe_combine
-          fma4(t, g0, ld4(y0 + 4 * c));
-          fma4(t, g1, ld4(y1 + 4 * c));
-          add4(v[i], t);
+      for (int i = 0; i < VPT; ++i) t[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int k = 0; k < a.comb_top; ++k) {
+        const float g = a.comb_gates[(size_t)a.comb_top * src + k];
+        const float* y = a.comb_y + (size_t)a.comb_row_of[(size_t)a.comb_top * src + k] * H;
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {
+          const int c = threadIdx.x + i * blockDim.x;
+          if (c < n4) fma4(t[i], g, ld4(y + 4 * c));
         }
       }
+#pragma unroll
+      for (int i = 0; i < VPT; ++i) add4(v[i], t[i]);
     }
     if (pending) {
 #pragma unroll
@@ -379,19 +381,19 @@ row_norm_cluster_kernel(const __grid_constant__ RowArgs a, const int vec_per_blo
     }
   }
   if (a.comb_y) {
-    const int r0 = a.comb_row_of[2 * src], r1 = a.comb_row_of[2 * src + 1];
-    const float g0 = a.comb_gates[2 * src], g1 = a.comb_gates[2 * src + 1];
-    const float* y0 = a.comb_y + (size_t)r0 * H;
-    const float* y1 = a.comb_y + (size_t)r1 * H;
+    float4 t[VPT];                                   // gated rows summed in the order of the choices, then added
 #pragma unroll
-    for (int i = 0; i < VPT; ++i) {
-      if (ok[i]) {
-        float4 t = make_float4(0.f, 0.f, 0.f, 0.f);   // g0*y0 + g1*y1 first, then added: the order of moe_combine
-        fma4(t, g0, ld4(y0 + 4 * col[i]));
-        fma4(t, g1, ld4(y1 + 4 * col[i]));
-        add4(v[i], t);
-      }
+    for (int i = 0; i < VPT; ++i) t[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int k = 0; k < a.comb_top; ++k) {
+      const float g = a.comb_gates[(size_t)a.comb_top * src + k];
+      const float* y = a.comb_y + (size_t)a.comb_row_of[(size_t)a.comb_top * src + k] * H;
+#pragma unroll
+      for (int i = 0; i < VPT; ++i)
+        if (ok[i]) fma4(t[i], g, ld4(y + 4 * col[i]));
     }
+#pragma unroll
+    for (int i = 0; i < VPT; ++i)
+      if (ok[i]) add4(v[i], t[i]);
   }
   if (pending) {
 #pragma unroll
@@ -564,13 +566,13 @@ extern "C" int flint_row_norm_set_cluster_rows(int rows) {
 // x [T, H] float32 residual stream, updated in place if anything is pending.
 // rows: number of output rows (T, or the length of row_index if given; then x rows are gathered).
 // pending: partials [n_partials][T][H] (stride partial_stride floats) + add_bias [H]; and/or
-//          comb_y [2T, H] with comb_row_of [T, 2] and comb_gates [T, 2].
+//          comb_y [comb_top T, H] with comb_row_of [T, comb_top] and comb_gates [T, comb_top].
 // gamma NULL: only apply the pending additions.  wr != NULL (router weights [E, H], bf16 or f32):
 // also fill expert_ids [rows, 2] and gates [rows, 2] (and router_logits [rows, E] if given); then row_index
 // must be NULL.
 extern "C" int flint_row_norm(float* x, const int* row_index, int rows, int H, const float* partials,
                               int n_partials, long long partial_stride, const float* add_bias,
-                              const float* comb_y, const int* comb_row_of, const float* comb_gates,
+                              const float* comb_y, const int* comb_row_of, const float* comb_gates, int comb_top,
                               const float* gamma, const float* beta, float eps, int mode, float* out_f32,
                               void* out_bf16, const void* wr, int w_dtype, int E, float jitter_eps,
                               int* expert_ids, float* gates, float* router_logits, cudaStream_t stream) {
@@ -578,13 +580,14 @@ extern "C" int flint_row_norm(float* x, const int* row_index, int rows, int H, c
   if (H <= 0 || (H & 3) || H > 4 * 1024 * MAX_VPT) return fail("row_norm: width %d (multiples of 4 up to %d)", H, 4096 * MAX_VPT);
   if (gamma && !out_f32 && !out_bf16 && !wr) return fail("row_norm: no output given");
   if (mode != 0 && mode != 1) return fail("row_norm: unknown mode %d", mode);
+  if (comb_y && comb_top < 1) return fail("row_norm: %d expert rows a token", comb_top);
   if (wr && (E < 2 || E > MAX_E)) return fail("row_norm: %d experts (2..%d)", E, MAX_E);
   if (wr && (row_index || !gamma || !expert_ids || !gates)) return fail("row_norm: the router needs a norm and all rows");
   if (wr && (((uintptr_t)wr & 15) != 0)) return fail("row_norm: router weights must be 16-byte aligned");
   RowArgs a;
   a.x = x; a.row_index = row_index;
   a.partials = partials; a.n_partials = n_partials; a.partial_stride = partial_stride; a.add_bias = add_bias;
-  a.comb_y = comb_y; a.comb_row_of = comb_row_of; a.comb_gates = comb_gates;
+  a.comb_y = comb_y; a.comb_row_of = comb_row_of; a.comb_gates = comb_gates; a.comb_top = comb_top;
   a.gamma = gamma; a.beta = beta; a.eps = eps; a.mode = mode;
   a.out_f32 = out_f32; a.out_bf16 = (__nv_bfloat16*)out_bf16;
   a.wr = wr; a.E = E; a.jitter_eps = jitter_eps; a.expert_ids = expert_ids; a.gates = gates;

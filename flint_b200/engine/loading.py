@@ -21,15 +21,17 @@ def expected_from_config(config: dict, with_fused=False):
     from ..registry import POSITION_ENCODINGS
     embed_position = (POSITION_ENCODINGS.get(spec.embed_position.kind)(spec.embed_position.params, ctx)
                       if spec.embed_position is not None else None)
-    expected = expected_tensors(spec, layers, NORMS.get(spec.final_norm.kind)(spec.final_norm.params, ctx), embed_position)
+    from .model import build_embed_additions
+    expected = expected_tensors(spec, layers, NORMS.get(spec.final_norm.kind)(spec.final_norm.params, ctx), embed_position,
+                                build_embed_additions(spec, ctx))
     return (spec, expected, fused_tensors(layers)) if with_fused else (spec, expected)
 
 
 def write_random_model(out_dir, config: dict, seed: int = 0, dtype=torch.bfloat16):
     """Random-weights mode: write ``config.json`` and ``model.safetensors`` for a
     configuration and a seed (weights and biases N(0, 0.02), norm scales 1 + N(0, 0.1))."""
-    _, expected = expected_from_config(config)
-    return write_model_folder(out_dir, config, expected, seed, dtype=dtype)
+    spec, expected = expected_from_config(config)
+    return write_model_folder(out_dir, config, expected, seed, dtype=dtype, stored_names=spec.stored_names)
 
 
 def random_model(config: dict, seed: int = 0, *, dtype="bfloat16", store_dtype=None, on_device=False, **model_kw) -> Model:

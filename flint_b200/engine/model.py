@@ -22,9 +22,9 @@ from ..config.spec import ModelSpec
 from ..errors import ConfigError, ModelError
 from ..parts.base import BuildContext, matmul_dtype
 from ..parts.block import run_norm
-from ..registry import ARCHITECTURES, BLOCKS, FEED_FORWARDS, MIXERS, NORMS, POSITION_ENCODINGS
+from ..registry import ARCHITECTURES, BLOCKS, EMBED_ADDITIONS, FEED_FORWARDS, MIXERS, NORMS, POSITION_ENCODINGS
 from ..weights.loader import load_tensors
-from ..weights.sources import SafetensorsSource, WeightSpec
+from ..weights.sources import RenamedSource, SafetensorsSource, WeightSpec
 from .step import StepEntry, StepStaging
 
 def registry_for_role(role: str):
@@ -67,12 +67,20 @@ class Layer:
             part.load({name: tensors[pre + name] for name in part.weights() if pre + name in tensors})
 
 
-def expected_tensors(spec: ModelSpec, layers, final_norm, embed_position=None) -> dict:
+def build_embed_additions(spec: ModelSpec, ctx) -> list:
+    """[(part, tensor-name prefix)] for ``spec.embed_additions``."""
+    return [(EMBED_ADDITIONS.get(ps.kind)(ps.params, ctx), prefix) for ps, prefix in spec.embed_additions]
+
+
+def expected_tensors(spec: ModelSpec, layers, final_norm, embed_position=None, embed_additions=()) -> dict:
     """Every tensor name the model reads, with its shape and role."""
     exp = {spec.embed_name + "weight": WeightSpec((spec.vocab_size, spec.hidden_size))}
     if embed_position is not None:
         for name, ws in embed_position.weights().items():
             exp[spec.embed_position_name + name] = ws
+    for part, prefix in embed_additions:
+        for name, ws in part.weights().items():
+            exp[prefix + name] = ws
     for layer in layers:
         exp.update(layer.weights())
     for name, ws in final_norm.weights().items():
@@ -107,7 +115,10 @@ class Model:
             from ..csrc.ops import get_ops
             ops = get_ops(self.device)
         self.ops = ops
-        self.ctx = BuildContext(ops=ops, device=self.device, compute=dtype)
+        self.max_context = int(max_context or spec.max_positions)
+        if self.max_context > spec.max_positions:
+            raise ConfigError(f"max_context {self.max_context} exceeds the model's {spec.max_positions} positions")
+        self.ctx = BuildContext(ops=ops, device=self.device, compute=dtype, max_context=self.max_context)
         self.layers = [Layer(ls, self.ctx) for ls in spec.layers]
         self.final_norm = NORMS.get(spec.final_norm.kind)(spec.final_norm.params, self.ctx)
         self.embed_position = None
@@ -117,7 +128,8 @@ class Model:
                 raise ConfigError(f"position encoding {spec.embed_position.kind!r} cannot act on the embedded rows "
                                   f"(it has no after_embedding)")
 
-        expected = expected_tensors(spec, self.layers, self.final_norm, self.embed_position)
+        self.embed_additions = build_embed_additions(spec, self.ctx)
+        expected = expected_tensors(spec, self.layers, self.final_norm, self.embed_position, self.embed_additions)
         self.expected = expected
         tensors = load_tensors(source, expected, dtype, self.device, fused_tensors(self.layers))
         self.embed_table = tensors[spec.embed_name + "weight"]
@@ -126,6 +138,8 @@ class Model:
         self.final_norm.load({n: tensors[spec.final_norm_name + n] for n in self.final_norm.weights()})
         if self.embed_position is not None:
             self.embed_position.load({n: tensors[spec.embed_position_name + n] for n in self.embed_position.weights()})
+        for part, prefix in self.embed_additions:
+            part.load({n: tensors[prefix + n] for n in part.weights()})
         for layer in self.layers:
             layer.load(tensors)
         del tensors
@@ -149,9 +163,10 @@ class Model:
             ss = mixer.state_spec()
             if ss is not None:
                 state_calls[i] = ss
-        self.max_context = int(max_context or spec.max_positions)
-        if self.max_context > spec.max_positions:
-            raise ConfigError(f"max_context {self.max_context} exceeds the model's {spec.max_positions} positions")
+        for k, (part, _) in enumerate(self.embed_additions):       # state of the additions to the embedded rows
+            ss = part.state_spec()
+            if ss is not None:
+                state_calls[("embed", k)] = ss
         if n_pages is None:
             n_pages = max_slots * -(-self.max_context // page_size)
         cache_dtype = torch.bfloat16 if dtype == "bfloat16" else torch.float32
@@ -171,6 +186,7 @@ class Model:
         # key-range split), and replayed: their hundreds of small launches would otherwise be bound by the host
         self.use_graphs = (use_graphs and self.device.type == "cuda" and self.final_norm.graph_safe
                            and (self.embed_position is None or self.embed_position.graph_safe)
+                           and all(part.graph_safe for part, _ in self.embed_additions)
                            and all(p.graph_safe for layer in self.layers for p in layer.parts.values()))
         self._graphs = {}
         self._graph_pool = None         # one memory pool for all captured steps: only one of them runs at a time
@@ -188,6 +204,12 @@ class Model:
     def eos_token_ids(self):
         return tuple(self.spec.eos_token_ids)
 
+    def _parts_with_tensors(self):
+        for part, _ in self.embed_additions:
+            yield part
+        for layer in self.layers:
+            yield from layer.parts.values()
+
     def weight_bytes(self):
         seen, total = set(), 0
         def add(t):
@@ -196,11 +218,10 @@ class Model:
                 seen.add(t.data_ptr())
                 total += t.numel() * t.element_size()
         add(self.embed_table); add(self.head_weight); add(self.head_bias)
-        for layer in self.layers:
-            for part in layer.parts.values():
-                for v in vars(part).values():
-                    if isinstance(v, torch.Tensor):
-                        add(v)
+        for part in self._parts_with_tensors():
+            for v in vars(part).values():
+                if isinstance(v, torch.Tensor):
+                    add(v)
         return total
 
     # ------------------------------------------------------------------ the step function
@@ -214,7 +235,7 @@ class Model:
                     raise ModelError(f"slot {e.slot}: pages do not cover positions up to "
                                      f"{e.start_pos + len(e.tokens) - 1}")
         self.cache.sync()
-        step = self.staging.pack(entries, self.spec.vocab_size, self.spec.max_positions)
+        step = self.staging.pack(entries, self.spec.vocab_size, self.max_context)
         if step.n_fed and self.fed_from is None:
             raise ModelError("an entry's token is fed from the sampler's output, but this kernel set keeps none")
         step.record = record
@@ -265,6 +286,8 @@ class Model:
             ops.embed(step.ids, self.embed_table, h, spec.embed_scale)
         if self.embed_position is not None:
             self.embed_position.after_embedding(h, step)
+        for k, (part, _) in enumerate(self.embed_additions):
+            part.forward(h, step, self.cache.state_of(("embed", k)), fed_from=self.fed_from)
         carry = None     # an addition to h that a layer left for the next norm to apply
         for i, call in enumerate(self.order):
             layer = self.layers[call.layer]
@@ -310,9 +333,14 @@ def read_config(model_dir) -> dict:
 
 
 def architecture_of(config: dict):
+    """The architecture class a config.json names: the first entry of ``architectures``, or the string under
+    ``architecture``."""
     archs = config.get("architectures")
+    if archs is None and isinstance(config.get("architecture"), str):
+        archs = [config["architecture"]]
     if not archs or not isinstance(archs, list) or not isinstance(archs[0], str):
-        raise ConfigError("config.json has no 'architectures' entry; registered: " + ", ".join(ARCHITECTURES.names()))
+        raise ConfigError("config.json names no architecture ('architectures' or 'architecture'); registered: "
+                          + ", ".join(ARCHITECTURES.names()))
     return ARCHITECTURES.get(archs[0])
 
 
@@ -322,4 +350,5 @@ def load_model(model_dir, **kw) -> Model:
     cfg = read_config(model_dir)
     arch = architecture_of(cfg)
     spec = arch.model_spec(arch.parse_config(cfg))
-    return Model(spec, SafetensorsSource(model_dir), **kw)
+    source = SafetensorsSource(model_dir)
+    return Model(spec, RenamedSource(source, spec.stored_names) if spec.stored_names else source, **kw)

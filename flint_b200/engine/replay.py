@@ -20,9 +20,15 @@ class Replayer:
         if page_size <= 0 or 64 % page_size:
             raise ModelError(f"--page-size must divide 64, got {page_size}")
         n_pages = max(1, -(-int(max_tokens) // page_size))
-        self.model = model or load_model(model_dir, dtype=dtype, device=device, ops=ops, page_size=page_size,
-                                         n_pages=n_pages, max_slots=max_requests,
-                                         max_step_tokens=max(int(max_tokens), 64))
+        if model is None:
+            # no request can be longer than the pool; an architecture without a limit of its own is built for that
+            from .model import architecture_of, read_config
+            arch = architecture_of(read_config(model_dir))
+            limit = arch.model_spec(arch.parse_config(read_config(model_dir))).max_positions
+            model = load_model(model_dir, dtype=dtype, device=device, ops=ops, page_size=page_size, n_pages=n_pages,
+                               max_slots=max_requests, max_step_tokens=max(int(max_tokens), 64),
+                               max_context=min(limit, n_pages * page_size))
+        self.model = model
         self.live = {}      # request id -> [slot, tokens run]
 
     def run_step(self, entries, end=(), record=None):

@@ -26,6 +26,8 @@ PositionEncoding  ``rotary_dim``, ``style`` ("half": dims i and i + rotary_dim/2
               ``ModelSpec.embed_position`` instead has ``after_embedding(h, step)`` and adds to the embedded rows.
 Block         ``forward(residual, step, cache, state, writes_cache)``: the arrangement of
               the parts of one layer.
+EmbedAddition ``weights()``, ``state_spec()`` (per-request state, or None), ``forward(h, step, state)``: adds to the
+              embedded rows h [T, H] in place (a table row chosen by the token and its predecessor, and the like).
 """
 from __future__ import annotations
 
@@ -41,8 +43,8 @@ class Pending:
     """An addition to the residual stream that its producer has not applied: the next norm's
     kernel applies it while it reads the row anyway (or ``ops.apply_pending`` does, for a norm
     that cannot).  Either partial sums of a product whose K range was split
-    (``partials`` [S, T, H] float32, plus an optional ``bias`` [H]), or the two selected experts'
-    outputs (``y`` [2T, H] with ``row_of`` [T, 2] and ``gates`` [T, 2]), or both."""
+    (``partials`` [S, T, H] float32, plus an optional ``bias`` [H]), or the selected experts'
+    outputs (``y`` [kT, H] with ``row_of`` [T, k] and ``gates`` [T, k], k choices a token), or both."""
     partials: torch.Tensor | None = None
     bias: torch.Tensor | None = None
     y: torch.Tensor | None = None
@@ -70,6 +72,7 @@ class BuildContext:
     device: torch.device
     compute: str                   # "bfloat16" or "float32"
     shared: dict = field(default_factory=dict)   # things built once per model (position tables)
+    max_context: int | None = None               # positions the model is built to serve (None: the architecture's limit)
 
     @property
     def act_dtype(self):
@@ -139,6 +142,16 @@ class Norm(Part):
     supports_router = False
 
     def forward(self, x, want, row_index=None, pending=None, router=None):
+        raise NotImplementedError
+
+
+class EmbedAddition(Part):
+    """Something added to the embedded rows before the first layer; it may keep fixed-size state per request."""
+
+    def state_spec(self):
+        return None
+
+    def forward(self, h, step, state):
         raise NotImplementedError
 
 

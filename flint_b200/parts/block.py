@@ -2,7 +2,7 @@
 
 ``prenorm``: h += mixer(norm1(h)); h += ffn(norm2(h)) -- the reference's decoder layer
 (crates/thuban_architectures/src/transformer/forward.rs:102-440) and Phi-MoE's.
-``parallel``: h += mixer(norm1(h)) + ffn(norm1(h)) with one shared norm.
+``parallel``: h += mixer(norm1(h)) + ffn(norm1(h)) with one shared norm (the feed-forward may be absent).
 An arrangement only orders parts; it does not know what they are.
 """
 from __future__ import annotations
@@ -10,6 +10,7 @@ from __future__ import annotations
 import torch
 
 from ..registry import BLOCKS
+from .base import Pending
 
 
 def run_norm(norm, residual, want, pending=None, router=None, row_index=None):
@@ -67,13 +68,28 @@ class PreNormBlock(Block):
         return ffn.forward(x, residual, step, routed=routed) if routed is not None else ffn.forward(x, residual, step)
 
 
+def merge_pending(part, residual, first, second):
+    """One Pending for two parts' additions: partial sums of a product from one and gated expert rows from the
+    other travel together to the next norm; what cannot be merged is applied right away."""
+    if first is None or second is None:
+        return first if second is None else second
+    for a, b in ((first, second), (second, first)):
+        if a.y is None and b.partials is None and b.bias is None:
+            return Pending(partials=a.partials, bias=a.bias, y=b.y, row_of=b.row_of, gates=b.gates)
+    settle(part, residual, first)
+    return second
+
+
 @BLOCKS.register("parallel")
 class ParallelBlock(Block):
-    roles = ("norm1", "mixer", "ffn")
+    roles = ("norm1", "mixer")        # "ffn" is optional: a layer may be a mixer alone
 
     def forward(self, residual, step, cache, state, writes_cache=True, carry=None):
         p = self.parts
-        want = tuple(set(p["mixer"].input_dtypes()) | set(p["ffn"].input_dtypes()))
+        ffn = p.get("ffn")
+        want = tuple(set(p["mixer"].input_dtypes()) | set(ffn.input_dtypes() if ffn is not None else ()))
         x, _ = run_norm(p["norm1"], residual, want, carry)
-        settle(p["mixer"], residual, p["mixer"].forward(x, residual, step, cache, state, writes_cache))
-        return p["ffn"].forward(x, residual, step)
+        mixed = p["mixer"].forward(x, residual, step, cache, state, writes_cache)
+        if ffn is None:
+            return mixed
+        return merge_pending(p["mixer"], residual, mixed, ffn.forward(x, residual, step))

@@ -7,8 +7,8 @@ The choice is made per position, as the reference does
 (crates/thuban_model/src/ops/rope.rs:52-87), so a cached key never has to be rotated
 again and the logits do not depend on how a prompt was cut.  The LongRoPE magnitude
 scale (short_mscale / long_mscale, again per position) multiplies cos and sin; the
-reference has no such scale.  The rotation itself (NeoX half-split) is done by the
-kernel that also writes keys and values into the cache.
+reference has no such scale.  The rotation itself (dims i and i + rot/2 together, or, with
+style "interleaved", dims 2i and 2i + 1) is done by the kernel that also writes the cache.
 """
 from __future__ import annotations
 
@@ -21,8 +21,9 @@ from .base import PositionEncoding
 
 @POSITION_ENCODINGS.register("rope")
 class RotaryEncoding(PositionEncoding):
-    """params: rotary_dim, theta, max_positions, and for LongRoPE: short_factor,
-    long_factor, original_max_positions, short_mscale, long_mscale."""
+    """params: rotary_dim, theta, max_positions, style ("half", the default, or "interleaved"), and for LongRoPE:
+    short_factor, long_factor, original_max_positions, short_mscale, long_mscale.  The tables cover the positions
+    the model is built to serve (``BuildContext.max_context``) when that is fewer than ``max_positions``."""
 
     def __init__(self, params, ctx):
         super().__init__(params, ctx)
@@ -31,6 +32,11 @@ class RotaryEncoding(PositionEncoding):
             raise ConfigError(f"rotary_dim must be even and positive, got {self.rotary_dim}")
         self.theta = float(params["theta"])
         self.max_positions = int(params["max_positions"])
+        if getattr(ctx, "max_context", None):
+            self.max_positions = min(self.max_positions, int(ctx.max_context))
+        self.style = params.get("style", "half")
+        if self.style not in ("half", "interleaved"):
+            raise ConfigError(f"rotation style must be 'half' or 'interleaved', got {self.style!r}")
         self._tables = None
 
     def tables(self):

@@ -49,4 +49,5 @@ FEED_FORWARDS = Registry("feed-forward")
 NORMS = Registry("norm")
 POSITION_ENCODINGS = Registry("position encoding")
 BLOCKS = Registry("block arrangement")
+EMBED_ADDITIONS = Registry("embedding addition")
 ARCHITECTURES = Registry("architecture")

@@ -71,10 +71,11 @@ def load_tensors(source, expected: dict, compute: str, device, fused: dict | Non
 
 
 def write_model_folder(out_dir, config_dict: dict, expected: dict, seed: int,
-                       dtype=torch.bfloat16, name_prefix="model.", head_prefix="lm_head."):
+                       dtype=torch.bfloat16, name_prefix="model.", head_prefix="lm_head.", stored_names=None):
     """Random-weights mode: write ``config.json`` and ``model.safetensors`` for a
     configuration and a seed.  Names get the customary ``model.`` prefix, except the
-    output head."""
+    output head; an architecture whose checkpoints name tensors in their own way
+    (``stored_names``: the parts' name -> the stored name) gets exactly those names."""
     out_dir = Path(out_dir)
     out_dir.mkdir(parents=True, exist_ok=True)
     (out_dir / "config.json").write_text(json.dumps(config_dict, indent=1))
@@ -91,7 +92,10 @@ def write_model_folder(out_dir, config_dict: dict, expected: dict, seed: int,
 
     tensors = {}
     for name in expected:
-        stored = name if name.startswith(head_prefix) else name_prefix + name
+        if stored_names:
+            stored = stored_names.get(name, name)
+        else:
+            stored = name if name.startswith(head_prefix) else name_prefix + name
         tensors[stored] = _Lazy(name)
     save_safetensors(out_dir / "model.safetensors", tensors, metadata={"format": "pt", "seed": seed})
     return out_dir

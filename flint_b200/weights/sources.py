@@ -80,6 +80,28 @@ class SafetensorsSource:
             f.close()
 
 
+class RenamedSource:
+    """A source whose tensors the model knows under other names: ``stored`` maps the model's name of a tensor to
+    the name the source has it under (names not in the map are the same on both sides)."""
+
+    def __init__(self, source, stored: dict):
+        self.source = source
+        self._stored = dict(stored)
+        self._model_name = {v: k for k, v in self._stored.items()}
+
+    def names(self):
+        return [self._model_name.get(n, n) for n in self.source.names()]
+
+    def shape(self, name):
+        return self.source.shape(self._stored.get(name, name))
+
+    def dtype(self, name):
+        return self.source.dtype(self._stored.get(name, name))
+
+    def read(self, name, spec=None, device="cpu"):
+        return self.source.read(self._stored.get(name, name), spec, device)
+
+
 class RandomSource:
     """Seeded random tensors for a given set of specs.  Every tensor has its own
     generator seeded by (seed, crc32(name)), so one tensor's values do not depend on

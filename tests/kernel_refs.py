@@ -126,10 +126,11 @@ class RefOps:
         out.copy_(rows)
 
     def moe_combine(self, h, y, row_of, gates):
-        r = row_of.view(-1, 2).long()
-        g = gates.view(-1, 2).to(self.cd)
+        k = row_of.numel() // h.shape[0]
+        r = row_of.view(-1, k).long()
+        g = gates.view(-1, k).to(self.cd)
         yy = y.to(self.cd)
-        h.add_((g[:, 0:1] * yy[r[:, 0]] + g[:, 1:2] * yy[r[:, 1]]).to(h.dtype))
+        h.add_(sum(g[:, i:i + 1] * yy[r[:, i]] for i in range(k)).to(h.dtype))
 
     # ------------------------------------------------------------------ matrix products
     def gemm(self, x, w, out, bias=None, accumulate=False):
@@ -190,8 +191,104 @@ class RefOps:
                 res[t, h] = torch.softmax(s, 0) @ v[:, h // G, :]
         out.copy_(res.reshape(T, nq * hd).to(out.dtype))
 
-    def moe_tile_rows(self, n_tokens, n_experts, weight_dtype):
+    def moe_tile_rows(self, n_tokens, n_experts, weight_dtype, top=2):
         return 64
+
+    # ------------------------------------------------------------------ attention over a cached latent
+    def head_products(self, x, w, out):
+        out.copy_(torch.einsum("thk,hnk->thn", x.to(self.cd), w.to(self.cd)).to(out.dtype))
+
+    def latent_prepare(self, proj, pos, slot, cos, sin, rot_dims, style, norm_w, eps, q_plain, qa, cache, H, D, R, C,
+                       write_kv, status):
+        x = (proj.to(self.cd).sum(0) if proj.dim() == 3 else proj.to(self.cd))
+        T = x.shape[0]
+        p = pos.long()
+        half = rot_dims // 2
+
+        def rotate(v):          # [T, ..., R]
+            if rot_dims == 0:
+                return v
+            shape = [T] + [1] * (v.dim() - 2) + [half]
+            c, s_ = cos[p].to(self.cd).view(shape), sin[p].to(self.cd).view(shape)
+            if style == "interleaved":
+                a, b = v[..., 0:rot_dims:2], v[..., 1:rot_dims:2]
+                both = torch.stack([a * c - b * s_, b * c + a * s_], -1).reshape(*v.shape[:-1], rot_dims)
+            else:
+                a, b = v[..., :half], v[..., half:rot_dims]
+                both = torch.cat([a * c - b * s_, b * c + a * s_], -1)
+            return torch.cat([both, v[..., rot_dims:]], -1)
+        q = x[:, :H * (D + R)].view(T, H, D + R)
+        q_plain.copy_(q[..., :D].to(q_plain.dtype))
+        qa[..., C:] = rotate(q[..., D:]).to(qa.dtype)
+        if not write_kv:
+            return
+        lat = x[:, H * (D + R):]
+        c = lat[:, :C]
+        c = c / torch.sqrt((c * c).mean(-1, keepdim=True) + eps) * norm_w.to(self.cd)
+        row = torch.zeros(T, cache.k.shape[-1], dtype=self.cd)
+        row[:, :C] = c
+        row[:, C:C + R] = rotate(lat[:, C:C + R])
+        P = cache.page_size
+        pages = cache.block_table[slot.long(), p // P].long()
+        assert (pages >= 0).all(), "write to a position without a page"
+        cache.k[pages, 0, p % P, :] = row.to(cache.k.dtype)
+
+    def latent_attention(self, qa, cache, step, out, H, C, window, scale, splits=None, rows=None):
+        T, Dk = qa.shape[0], qa.shape[2]
+        P = cache.page_size
+        for t in (range(T) if rows is None else rows.tolist()):
+            p = int(step.pos[t])
+            lo = max(0, p + 1 - window) if window else 0
+            js = torch.arange(lo, p + 1)
+            pages = cache.block_table[int(step.slot[t]), js // P].long()
+            assert (pages >= 0).all(), f"row {t}: key without a page"
+            k = cache.k[pages, 0, js % P, :].to(self.cd)            # [n, row]
+            s = (qa[t].to(self.cd) @ k[:, :Dk].T) * scale            # [H, n]
+            out[t] = (torch.softmax(s, -1) @ k[:, :C]).to(out.dtype)
+
+    def pair_embed_add(self, ids, pos, slot, last, table, out, mul_prev, mul_cur, fed_rows=None, fed_from=None):
+        ids = ids.long().clone()
+        if fed_rows is not None:
+            fed = fed_rows.long()
+            ids = torch.where(fed >= 0, fed_from.long()[fed.clamp(min=0)], ids)
+        buckets = table.shape[0] - 1
+        T = ids.numel()
+        rows = []
+        for r in range(T):
+            if int(pos[r]) == 0:
+                rows.append(buckets)
+                continue
+            first = r == 0 or int(slot[r - 1]) != int(slot[r])
+            prev = int(last[int(slot[r])]) if first else int(ids[r - 1])
+            rows.append((prev * mul_prev + int(ids[r]) * mul_cur) % buckets)
+        out.add_(table[torch.tensor(rows, dtype=torch.long)].to(self.cd).to(out.dtype))
+        for r in range(T):
+            if r == T - 1 or int(slot[r + 1]) != int(slot[r]):
+                last[int(slot[r])] = int(ids[r])
+
+    def router_topk(self, x, wr, top, n_groups, keep, scale, expert_ids, gates, logits_out=None):
+        z = x.to(self.cd) @ wr.to(self.cd).T
+        if logits_out is not None:
+            logits_out.copy_(z.to(logits_out.dtype))
+        E = wr.shape[0]
+        per = E // n_groups
+        for t in range(x.shape[0]):
+            s = torch.softmax(z[t], -1)
+            allowed = torch.zeros(E, dtype=torch.bool)
+            gs = s.view(n_groups, per).max(-1).values.clone()
+            for _ in range(keep):
+                g = int(torch.argmax(gs))
+                allowed[g * per:(g + 1) * per] = True
+                gs[g] = -1.0
+            cand = s.masked_fill(~allowed, -1.0)
+            chosen = []
+            for _ in range(top):
+                e = int(torch.argmax(cand))
+                chosen.append(e)
+                cand[e] = -1.0
+            w = s[chosen]
+            expert_ids[t] = torch.tensor(chosen, dtype=torch.int32)
+            gates[t] = (w / (w.sum() + 1e-20) * scale).to(gates.dtype)
 
     # ------------------------------------------------------------------ routing
     def router_sparsemixer(self, x, wr, eps, expert_ids, gates, logits_out=None):
@@ -223,7 +320,7 @@ class RefOps:
         order = torch.argsort(ids, stable=True)
         row_of = torch.empty(n, dtype=torch.long)
         row_of[order] = torch.arange(n)
-        token_of = order // 2
+        token_of = order // (expert_ids.shape[-1] if expert_ids.dim() > 1 else 2)
         tiles_e, tiles_r = [], []
         for e in range(n_experts):
             for r in range(0, int(counts[e]), tile_rows):
@@ -232,8 +329,9 @@ class RefOps:
         max_tiles = n // tile_rows + min(n_experts, n)
         i32 = lambda t: torch.as_tensor(t, dtype=torch.int32)
         pad = lambda l: i32(l + [0] * (max_tiles - len(l)))
-        return MoePlan(n_experts, tile_rows, max_tiles, i32(counts), i32(offsets), i32(row_of).view(-1, 2),
-                       i32(token_of), pad(tiles_e), pad(tiles_r), i32([len(tiles_e)]))
+        top = expert_ids.shape[-1] if expert_ids.dim() > 1 else 2
+        return MoePlan(n_experts, tile_rows, max_tiles, i32(counts), i32(offsets), i32(row_of).view(-1, top),
+                       i32(token_of), pad(tiles_e), pad(tiles_r), i32([len(tiles_e)]), top)
 
     def moe_dispatch(self, expert_ids, n_experts, tile_rows, x):
         plan = self.moe_plan(expert_ids, n_experts, tile_rows)
