@@ -91,6 +91,17 @@ class LatentAttention(Mixer):
         # one row per token for all heads, no separate values: the latent is the start of the row
         return KVSpec(1, self.row_w, self.window, value_dim=0) if self.own_cache else None
 
+    def plan_step(self, step, captured):
+        """A batch of decoded tokens that is captured as a CUDA graph has its key ranges cut for a bucketed
+        context length (four buckets per doubling, at least 256 apart), so that the graph serves every step up
+        to that length; the bucket is part of the graph's key."""
+        if not captured or step.n_tokens != len(step.entries):
+            return None
+        kv = max(step.max_kv_len, 1)
+        gran = max(256, 1 << max(kv.bit_length() - 3, 0))
+        step.max_kv_len = -(-kv // gran) * gran
+        return (step.max_kv_len,)
+
     def forward(self, x, residual, step, cache, state, writes_cache=True):
         if cache is None:
             raise ModelError("latent attention needs a cache")
