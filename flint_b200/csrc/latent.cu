@@ -236,6 +236,213 @@ latent_attention_kernel(const TQ* __restrict__ qa, const TC* __restrict__ k_cach
       }
   }
 }
+// ---------------------------------------------------------------------------------------------
+// The same attention on the tensor cores (bfloat16 in, float32 scores, sums and outputs).
+//
+// A block of 8 warps takes up to 32 query rows, a row being one (token, head) pair: `nt` consecutive tokens
+// of the batch by `nh` heads.  All rows of a request attend over the same cached rows, so the block
+// streams tiles of 64 keys through shared memory once for all of them (tokens of different requests in a
+// block are worked one run after the other).  Per tile: warp (wm, wk) computes the scores of query rows
+// [16 wm, +16) against keys [16 wk, +16) with mma.sync m16n8k16 (Q and K through ldmatrix), the four
+// warps of a row tile agree on the new maximum and sum through shared memory, the probabilities go to
+// shared memory as bfloat16, and the warp then adds P V for ITS quarter of the latent dims (V is the start
+// of the key rows already in shared memory, through ldmatrix.trans): the output accumulator of 16 rows by
+// up to 128 dims stays in registers.  Causal and window masks are per row.  With n_splits > 1 the key
+// range of a run is cut and the pieces are merged by attention_combine_kernel.
+constexpr int TM = 32;        // query rows per block
+constexpr int KT = 64;        // keys per tile
+constexpr int TC_THREADS = 256;
+
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+template <int NTW>            // blocks of 8 latent dims per warp in the value phase: latent size <= 32 NTW
+__global__ void __launch_bounds__(TC_THREADS)
+latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ qa, const __nv_bfloat16* __restrict__ k_cache,
+                            const int* __restrict__ block_table, int max_pages, int page_size,
+                            const int* __restrict__ pos, const int* __restrict__ slot, __nv_bfloat16* __restrict__ out,
+                            float* __restrict__ scratch, int T, int H, int C, int Dk, int row_w, int Dkp, int window,
+                            float scale, int nt, int nh, int split_keys, int n_splits) {
+  using flint_attn::ldsm4;
+  using flint_attn::ldsm4t;
+  using flint_attn::mma16816;
+  extern __shared__ __align__(16) uint8_t smem_raw[];
+  const int QS = Dkp + 8;                                        // row stride of Qs and Ks (elements): odd in 16-byte units
+  constexpr int PS = KT + 8;
+  __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);
+  __nv_bfloat16* Ks = Qs + (size_t)TM * QS;
+  __nv_bfloat16* Ps = Ks + (size_t)KT * QS + 512;                // slack: the value phase may read columns past a row's end
+  float* redm = reinterpret_cast<float*>(Ps + TM * PS);          // [TM][4]
+  float* reds = redm + TM * 4;                                   // [TM][4]
+  long long* krow = reinterpret_cast<long long*>(reds + TM * 4); // [KT] cache row of each key of the tile, or -1
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int wm = warp >> 2, wk = warp & 3;
+  const int t_first = blockIdx.x * nt, h0 = blockIdx.y * nh, split = blockIdx.z;
+  const int ntok = min(nt, T - t_first), nhh = min(nh, H - h0);
+  const int r_lo = wm * 16 + (lane >> 2), r_hi = r_lo + 8;       // the two query rows of this lane's fragments
+  const int cpr = Dkp / 8;                                       // 16-byte units per staged row
+
+  int ta = 0;
+  while (ta < ntok) {
+    const int s = slot[t_first + ta];
+    int tb = ta + 1;
+    while (tb < ntok && slot[t_first + tb] == s && pos[t_first + tb] == pos[t_first + tb - 1] + 1) ++tb;
+    const int n_rows = (tb - ta) * nhh;
+    const int p_a = pos[t_first + ta], p_b = p_a + (tb - ta) - 1;
+    const int lo_run = window > 0 ? max(0, p_a + 1 - window) : 0;
+    const int lo = lo_run + split * split_keys;
+    const int hi = min(p_b + 1, lo + split_keys);
+    const int* bt = block_table + (size_t)s * max_pages;
+    // the run's query rows, zero beyond the row's width and beyond the run
+    for (int e = tid; e < TM * Dkp; e += TC_THREADS) {
+      const int r = e / Dkp, d = e - r * Dkp;
+      __nv_bfloat16 v = __float2bfloat16_rn(0.f);
+      if (r < n_rows && d < Dk) {
+        const int tok = t_first + ta + r / nhh, h = h0 + r % nhh;
+        v = qa[((size_t)tok * H + h) * Dk + d];
+      }
+      Qs[(size_t)r * QS + d] = v;
+    }
+    const int p_lo = p_a + r_lo / nhh, p_hi = p_a + r_hi / nhh;   // positions of this lane's rows (if they are in the run)
+    float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.f, l_hi = 0.f;
+    float o[NTW][4];
+#pragma unroll
+    for (int i = 0; i < NTW; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
+
+    for (int j0 = lo; j0 < hi; j0 += KT) {
+      if (tid < KT) {
+        const int j = j0 + tid;
+        long long row = -1;
+        if (j < hi) {
+          const int page = bt[j / page_size];
+          if (page >= 0) row = (long long)page * page_size + (j % page_size);
+        }
+        krow[tid] = row;
+      }
+      __syncthreads();
+      for (int c = tid; c < KT * cpr; c += TC_THREADS) {
+        const int jj = c / cpr, cu = c - jj * cpr;
+        const long long row = krow[jj];
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (row >= 0 && cu * 8 < row_w) v = *reinterpret_cast<const uint4*>(k_cache + row * row_w + cu * 8);
+        *reinterpret_cast<uint4*>(Ks + (size_t)jj * QS + cu * 8) = v;
+      }
+      __syncthreads();
+      // ---- scores of 16 rows x 16 keys
+      float sc[2][4];
+#pragma unroll
+      for (int n = 0; n < 2; ++n) { sc[n][0] = sc[n][1] = sc[n][2] = sc[n][3] = 0.f; }
+      {
+        const uint32_t qaddr = smem_addr(Qs + (size_t)(wm * 16 + (lane & 15)) * QS + (lane >> 4) * 8);
+        const uint32_t kaddr = smem_addr(Ks + (size_t)(wk * 16 + ((lane >> 4) << 3) + (lane & 7)) * QS + ((lane >> 3) & 1) * 8);
+        for (int kk = 0; kk < Dkp; kk += 16) {
+          uint32_t a0, a1, a2, a3, b0, b1, b2, b3;
+          ldsm4(qaddr + kk * 2, a0, a1, a2, a3);
+          ldsm4(kaddr + kk * 2, b0, b1, b2, b3);
+          mma16816(sc[0], a0, a1, a2, a3, b0, b1);
+          mma16816(sc[1], a0, a1, a2, a3, b2, b3);
+        }
+      }
+      float mx_lo = -INFINITY, mx_hi = -INFINITY;
+#pragma unroll
+      for (int n = 0; n < 2; ++n)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int j = j0 + wk * 16 + n * 8 + 2 * (lane & 3) + (i & 1);
+          const int r = i < 2 ? r_lo : r_hi, p = i < 2 ? p_lo : p_hi;
+          const bool seen = r < n_rows && j < hi && j <= p && (window <= 0 || j > p - window) && krow[j - j0] >= 0;
+          sc[n][i] = seen ? sc[n][i] * scale : -INFINITY;
+          if (i < 2) mx_lo = fmaxf(mx_lo, sc[n][i]); else mx_hi = fmaxf(mx_hi, sc[n][i]);
+        }
+      mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 1));
+      mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 2));
+      mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1));
+      mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
+      if ((lane & 3) == 0) { redm[r_lo * 4 + wk] = mx_lo; redm[r_hi * 4 + wk] = mx_hi; }
+      __syncthreads();
+      float mn_lo = m_lo, mn_hi = m_hi;
+#pragma unroll
+      for (int w = 0; w < 4; ++w) { mn_lo = fmaxf(mn_lo, redm[r_lo * 4 + w]); mn_hi = fmaxf(mn_hi, redm[r_hi * 4 + w]); }
+      const float al_lo = mn_lo > -INFINITY ? expf(m_lo - mn_lo) : 1.f;      // 0 while m is still -inf
+      const float al_hi = mn_hi > -INFINITY ? expf(m_hi - mn_hi) : 1.f;
+      float sum_lo = 0.f, sum_hi = 0.f;
+#pragma unroll
+      for (int n = 0; n < 2; ++n) {
+        const float p0 = sc[n][0] > -INFINITY ? expf(sc[n][0] - mn_lo) : 0.f;
+        const float p1 = sc[n][1] > -INFINITY ? expf(sc[n][1] - mn_lo) : 0.f;
+        const float p2 = sc[n][2] > -INFINITY ? expf(sc[n][2] - mn_hi) : 0.f;
+        const float p3 = sc[n][3] > -INFINITY ? expf(sc[n][3] - mn_hi) : 0.f;
+        sum_lo += p0 + p1;
+        sum_hi += p2 + p3;
+        const int col = wk * 16 + n * 8 + 2 * (lane & 3);
+        *reinterpret_cast<__nv_bfloat162*>(Ps + r_lo * PS + col) = __floats2bfloat162_rn(p0, p1);
+        *reinterpret_cast<__nv_bfloat162*>(Ps + r_hi * PS + col) = __floats2bfloat162_rn(p2, p3);
+      }
+      sum_lo += __shfl_xor_sync(0xffffffffu, sum_lo, 1);
+      sum_lo += __shfl_xor_sync(0xffffffffu, sum_lo, 2);
+      sum_hi += __shfl_xor_sync(0xffffffffu, sum_hi, 1);
+      sum_hi += __shfl_xor_sync(0xffffffffu, sum_hi, 2);
+      if ((lane & 3) == 0) { reds[r_lo * 4 + wk] = sum_lo; reds[r_hi * 4 + wk] = sum_hi; }
+      __syncthreads();
+      l_lo = l_lo * al_lo + (reds[r_lo * 4] + reds[r_lo * 4 + 1] + reds[r_lo * 4 + 2] + reds[r_lo * 4 + 3]);
+      l_hi = l_hi * al_hi + (reds[r_hi * 4] + reds[r_hi * 4 + 1] + reds[r_hi * 4 + 2] + reds[r_hi * 4 + 3]);
+      m_lo = mn_lo;
+      m_hi = mn_hi;
+      // ---- O += P V for this warp's dims [32 NTW wk / 4 ...): 16 rows x 8 NTW dims
+#pragma unroll
+      for (int i = 0; i < NTW; ++i) { o[i][0] *= al_lo; o[i][1] *= al_lo; o[i][2] *= al_hi; o[i][3] *= al_hi; }
+      {
+        const uint32_t paddr = smem_addr(Ps + (wm * 16 + (lane & 15)) * PS + (lane >> 4) * 8);
+        const uint32_t vaddr = smem_addr(Ks + (size_t)((((lane >> 3) & 1) << 3) + (lane & 7)) * QS + (lane >> 4) * 8);
+#pragma unroll
+        for (int ks = 0; ks < KT / 16; ++ks) {
+          uint32_t a0, a1, a2, a3;
+          ldsm4(paddr + ks * 32, a0, a1, a2, a3);
+#pragma unroll
+          for (int nb = 0; nb < NTW; nb += 2) {
+            const int col = (wk * NTW + nb) * 8;
+            if (col < C) {
+              uint32_t b0, b1, b2, b3;
+              ldsm4t(vaddr + (uint32_t)(((size_t)ks * 16 * QS + col) * 2), b0, b1, b2, b3);
+              mma16816(o[nb], a0, a1, a2, a3, b0, b1);
+              mma16816(o[nb + 1], a0, a1, a2, a3, b2, b3);
+            }
+          }
+        }
+      }
+      __syncthreads();
+    }
+    // ---- this run's rows go out
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int r = half ? r_hi : r_lo;
+      if (r < n_rows) {
+        const int tok = t_first + ta + r / nhh, h = h0 + r % nhh;
+        const float m = half ? m_hi : m_lo, l = half ? l_hi : l_lo;
+        if (n_splits == 1) {
+          const float inv = l > 0.f ? 1.0f / l : 0.f;
+          __nv_bfloat16* dst = out + ((size_t)tok * H + h) * C;
+#pragma unroll
+          for (int nb = 0; nb < NTW; ++nb) {
+            const int col = (wk * NTW + nb) * 8 + 2 * (lane & 3);
+            if (col < C) dst[col] = __float2bfloat16_rn(o[nb][2 * half] * inv);
+            if (col + 1 < C) dst[col + 1] = __float2bfloat16_rn(o[nb][2 * half + 1] * inv);
+          }
+        } else {
+          float* dst = scratch + (((size_t)tok * H + h) * n_splits + split) * (C + 2);
+#pragma unroll
+          for (int nb = 0; nb < NTW; ++nb) {
+            const int col = (wk * NTW + nb) * 8 + 2 * (lane & 3);
+            if (col < C) dst[col] = o[nb][2 * half];
+            if (col + 1 < C) dst[col + 1] = o[nb][2 * half + 1];
+          }
+          if (wk == 0 && (lane & 3) == 0) { dst[C] = m; dst[C + 1] = l; }
+        }
+      }
+    }
+    __syncthreads();
+    ta = tb;
+  }
+}
 }  // namespace
 
 // proj [S, T, W] float32 partial sums of [q | latent] (W = H (D + R) + (write_kv ? C + R : 0)); q_plain
@@ -297,6 +504,47 @@ extern "C" int flint_latent_attention(const void* qa, int q_dtype, const void* k
   FLINT_DISPATCH_DTYPE(q_dtype, TO,
       (flint_attn::attention_combine_kernel<TO><<<(unsigned)((long long)T * H), threads, 0, stream>>>(
           scratch, (TO*)out, C, n_splits, H, row_list)));
+  return check_launch("latent_attention (merge)");
+}
+
+// The same on the tensor cores: bfloat16 qa, cache and out.  Blocks take `nt` consecutive tokens of the batch by
+// `nh` heads (nt * nh <= 32).
+extern "C" int flint_latent_attention_mma(const void* qa, const void* k_cache, const int* block_table, int max_pages,
+                                          int page_size, const int* pos, const int* slot, void* out, int T, int H, int C,
+                                          int Dk, int row_w, int window, float scale, int nt, int nh, int split_keys,
+                                          int n_splits, float* scratch, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (C < 1 || C > 512) return fail("latent_attention: latent size %d (supported: 1..512)", C);
+  if (Dk < C || row_w < Dk || (row_w & 7)) return fail("latent_attention: bad row sizes C=%d Dk=%d row=%d", C, Dk, row_w);
+  if (nt < 1 || nh < 1 || nt * nh > TM) return fail("latent_attention: %d tokens by %d heads do not fit a block of %d rows", nt, nh, TM);
+  if (n_splits < 1 || split_keys < 1) return fail("latent_attention: bad split (%d keys, %d splits)", split_keys, n_splits);
+  if (n_splits > 1 && !scratch) return fail("latent_attention: splits need scratch memory");
+  if (((uintptr_t)k_cache & 15) != 0) return fail("latent_attention: the cache must be 16-byte aligned");
+  const int Dkp = (row_w + 15) / 16 * 16;
+  const int QS = Dkp + 8;
+  const size_t smem = ((size_t)TM * QS + (size_t)KT * QS + 512 + (size_t)TM * (KT + 8)) * sizeof(__nv_bfloat16) +
+                      (size_t)TM * 8 * sizeof(float) + KT * sizeof(long long);
+  if (smem > 220 * 1024) return fail("latent_attention: rows of %d numbers are too wide", row_w);
+  dim3 grid((T + nt - 1) / nt, (H + nh - 1) / nh, n_splits);
+  if (grid.y > 65535 || grid.z > 65535) return fail("latent_attention: too many head chunks or splits");
+#define LAUNCH(N)                                                                                                     \
+  do {                                                                                                                \
+    if (smem > 48 * 1024)                                                                                             \
+      cudaFuncSetAttribute(latent_attention_mma_kernel<N>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);  \
+    latent_attention_mma_kernel<N><<<grid, TC_THREADS, smem, stream>>>(                                               \
+        (const __nv_bfloat16*)qa, (const __nv_bfloat16*)k_cache, block_table, max_pages, page_size, pos, slot,        \
+        (__nv_bfloat16*)out, scratch, T, H, C, Dk, row_w, Dkp, window, scale, nt, nh, split_keys, n_splits);          \
+  } while (0)
+  if (C <= 64) LAUNCH(2);
+  else if (C <= 128) LAUNCH(4);
+  else if (C <= 256) LAUNCH(8);
+  else LAUNCH(16);
+#undef LAUNCH
+  int rc = check_launch("latent_attention (tensor cores)");
+  if (rc || n_splits == 1) return rc;
+  const int threads = C >= 128 ? 128 : 64;
+  flint_attn::attention_combine_kernel<__nv_bfloat16><<<(unsigned)((long long)T * H), threads, 0, stream>>>(
+      scratch, (__nv_bfloat16*)out, C, n_splits, H, nullptr);
   return check_launch("latent_attention (merge)");
 }
 

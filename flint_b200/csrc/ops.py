@@ -760,9 +760,11 @@ class CudaOps:
         keys = -(-(-(-max(span, 1) // n)) // 32) * 32
         return keys, -(-max(span, 1) // keys)
 
-    def latent_attention(self, qa, cache, step, out, H, C, window, scale, splits=None, rows=None):
+    def latent_attention(self, qa, cache, step, out, H, C, window, scale, splits=None, rows=None, kernel=None):
         """Every row's heads over its request's cached latent rows: qa [T, H, Dk] (key up-projection folded in)
-        -> out [T, H, C], the probability-weighted sum of the latents (causal, ``window`` 0 = all keys)."""
+        -> out [T, H, C], the probability-weighted sum of the latents (causal, ``window`` 0 = all keys).
+        bfloat16 rows run on the tensor cores (``kernel`` "mma"), everything else, and a list of ``rows``, on the
+        float32 pipes ("simt")."""
         _check(qa, "qa", dims=3)
         _check(out, "out", qa.dtype, 3)
         T, Dk = qa.shape[0], qa.shape[2]
@@ -770,10 +772,34 @@ class CudaOps:
         row_w = k.shape[-1]
         if qa.shape[1] != H or tuple(out.shape) != (T, H, C) or tuple(k.shape[1:]) != (1, P, row_w) or row_w < Dk:
             raise KernelError("latent_attention: shapes do not match")
+        span = min(step.max_kv_len, window) if window else step.max_kv_len
+        mma_ok = qa.dtype == torch.bfloat16 and k.dtype == torch.bfloat16 and rows is None and C <= 512 and row_w <= 1024
+        if kernel is None:
+            kernel = "mma" if mma_ok else "simt"
+        if kernel == "mma":
+            if not mma_ok:
+                raise KernelError("latent_attention: the tensor-core kernel takes bfloat16 rows of up to 512 latent dims, all rows")
+            nh = min(H, 32)
+            decode = T == len(getattr(step, "entries", ()))          # one token a request: a block per token
+            nt = 1 if decode else max(1, 32 // nh)
+            if splits is None:
+                blocks = -(-T // nt) * -(-H // nh)
+                n = max(1, min(-(-max(span, 1) // 128), (2 * self.sm_count) // blocks))
+                keys = -(-(-(-max(span, 1) // n)) // 64) * 64
+                splits = (keys, -(-max(span, 1) // keys))
+            keys, n = splits
+            if keys * n < span:
+                raise KernelError(f"latent_attention: {n} splits of {keys} keys do not cover {span} keys")
+            scratch = torch.empty(T * H * n * (C + 2), dtype=torch.float32, device=qa.device) if n > 1 else None
+            return self._run("latent", "flint_latent_attention_mma", _ptr(qa), _ptr(k), _ptr(cache.block_table),
+                             c_int(cache.block_table.shape[1]), c_int(P), _ptr(step.pos), _ptr(step.slot), _ptr(out),
+                             c_int(T), c_int(H), c_int(C), c_int(Dk), c_int(row_w), c_int(window), c_float(scale),
+                             c_int(nt), c_int(nh), c_int(keys), c_int(n), _ptr(scratch))
+        if kernel != "simt":
+            raise KernelError(f"latent_attention: unknown kernel {kernel!r}")
         if rows is not None:
             _check(rows, "rows", torch.int32, 1)
             T = rows.numel()
-        span = min(step.max_kv_len, window) if window else step.max_kv_len
         keys, n = splits if splits is not None else self.latent_attention_plan(T, H, span)
         if keys * n < span:
             raise KernelError(f"latent_attention: {n} splits of {keys} keys do not cover {span} keys")

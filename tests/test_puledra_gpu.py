@@ -79,12 +79,14 @@ def test_latent_attention_finds_planted_keys(ops, dtype, C, R, H):
     step = SimpleNamespace(pos=pos.to(DEV), slot=slot.to(DEV), max_kv_len=300)
     exp = dense_latent_attention(qa.cpu(), dense, pos, slot, C, Dk, 1.0)
     tol = 2e-5 if dtype == torch.float32 else 3e-2
-    for splits in (None, (64, 5), (304, 1), (32, 10)):
-        out = torch.zeros(len(cases), H, C, dtype=dtype, device=DEV)
-        ops.latent_attention(qa.to(DEV), view, step, out, H, C, 0, 1.0, splits=splits)
-        assert (out.double().cpu() - exp).abs().max() < tol, splits
-        for t, (s, p, j) in enumerate(cases):                # and it is the planted key's latent, not a neighbour's
-            assert (out[t].double().cpu() - dense[s][j, :C]).abs().max() < 5e-2 + tol
+    kernels = ("simt",) if dtype == torch.float32 else ("simt", "mma")
+    for kernel in kernels:
+        for splits in (None, (64, 5), (304, 1), (32, 10)):
+            out = torch.zeros(len(cases), H, C, dtype=dtype, device=DEV)
+            ops.latent_attention(qa.to(DEV), view, step, out, H, C, 0, 1.0, splits=splits, kernel=kernel)
+            assert (out.double().cpu() - exp).abs().max() < tol, (kernel, splits)
+            for t, (s, p, j) in enumerate(cases):                # and it is the planted key's latent, not a neighbour's
+                assert (out[t].double().cpu() - dense[s][j, :C]).abs().max() < 5e-2 + tol
     # a list of rows: the others stay as they were
     out = torch.full((len(cases), H, C), 7.0, dtype=dtype, device=DEV)
     some = torch.tensor([1, 4, 12], dtype=torch.int32, device=DEV)
@@ -92,6 +94,39 @@ def test_latent_attention_finds_planted_keys(ops, dtype, C, R, H):
     keep = torch.ones(len(cases), dtype=torch.bool)
     keep[some.cpu().long()] = False
     assert (out.cpu()[keep] == 7.0).all() and (out.double().cpu()[~keep] - exp[~keep]).abs().max() < tol
+
+
+@pytest.mark.parametrize("C,R,H", [(40, 8, 5), (64, 32, 6), (256, 64, 40), (512, 64, 16)])
+def test_latent_attention_tiles_of_consecutive_tokens(ops, C, R, H):
+    """The tensor-core kernel on portions of prompts: blocks hold several tokens of one request (each with its
+    own causal limit), the last tokens of one request beside the first of the next, and decoded tokens."""
+    P_, Dk = 16, C + R
+    row_w = -(-Dk // 8) * 8
+    lens = (150, 90, 40)
+    rows = [torch.randn(n, Dk) for n in lens]
+    view, dense = paged_rows(rows, row_w, P_, torch.bfloat16, seed=2)
+    # portions: slot 0 positions 100..149, slot 1 positions 0..89, slot 2 position 39 alone
+    pos = torch.tensor(list(range(100, 150)) + list(range(0, 90)) + [39], dtype=torch.int32)
+    slot = torch.tensor([0] * 50 + [1] * 90 + [2], dtype=torch.int32)
+    T = len(pos)
+    qa = (torch.randn(T, H, Dk) * (2.0 / math.sqrt(Dk))).to(torch.bfloat16)
+    exp = dense_latent_attention(qa, dense, pos, slot, C, Dk, 1.0)
+    step = SimpleNamespace(pos=pos.to(DEV), slot=slot.to(DEV), max_kv_len=150, entries=[0, 1, 2])
+    for splits in (None, (64, 3), (192, 1)):
+        out = torch.zeros(T, H, C, dtype=torch.bfloat16, device=DEV)
+        ops.latent_attention(qa.to(DEV), view, step, out, H, C, 0, 1.0, splits=splits, kernel="mma")
+        assert (out.double().cpu() - exp).abs().max() < 3e-2, splits
+    ref = torch.zeros(T, H, C, dtype=torch.bfloat16, device=DEV)
+    ops.latent_attention(qa.to(DEV), view, step, ref, H, C, 0, 1.0, kernel="simt")
+    assert (ref.double().cpu() - exp).abs().max() < 3e-2
+    # decoded tokens: one token a request
+    pos1 = torch.tensor([149, 89, 39], dtype=torch.int32)
+    slot1 = torch.tensor([0, 1, 2], dtype=torch.int32)
+    q1 = qa[[49, 139, 140]].contiguous()
+    step1 = SimpleNamespace(pos=pos1.to(DEV), slot=slot1.to(DEV), max_kv_len=150, entries=[0, 1, 2])
+    out = torch.zeros(3, H, C, dtype=torch.bfloat16, device=DEV)
+    ops.latent_attention(q1.to(DEV), view, step1, out, H, C, 0, 1.0, kernel="mma")
+    assert (out.double().cpu() - exp[[49, 139, 140]]).abs().max() < 3e-2
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
@@ -111,14 +146,15 @@ def test_latent_attention_window_edges(ops, dtype):
         qa[t] = 40.0 * aim / (aim.norm() ** 2)
     qa = qa.to(dtype)
     step = SimpleNamespace(pos=pos.to(DEV), slot=slot.to(DEV), max_kv_len=100)
-    out = torch.zeros(6, H, C, dtype=dtype, device=DEV)
-    ops.latent_attention(qa.to(DEV), view, step, out, H, C, W, 1.0)
     exp = dense_latent_attention(qa.cpu(), dense, pos, slot, C, Dk, 1.0, window=W)
     tol = 2e-5 if dtype == torch.float32 else 3e-2
-    assert (out.double().cpu() - exp).abs().max() < tol
-    for t, j in enumerate(aims):
-        hit = (out[t].double().cpu() - dense[0][j, :C]).abs().max() < 5e-2 + tol
-        assert bool(hit) == (t % 2 == 0)
+    for kernel in (("simt",) if dtype == torch.float32 else ("simt", "mma")):
+        out = torch.zeros(6, H, C, dtype=dtype, device=DEV)
+        ops.latent_attention(qa.to(DEV), view, step, out, H, C, W, 1.0, kernel=kernel)
+        assert (out.double().cpu() - exp).abs().max() < tol
+        for t, j in enumerate(aims):
+            hit = (out[t].double().cpu() - dense[0][j, :C]).abs().max() < 5e-2 + tol
+            assert bool(hit) == (t % 2 == 0)
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
