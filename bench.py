@@ -419,6 +419,93 @@ def run_tiny(which, reps=5):
             "data": "synthetic: seeded random weights, uniform-random token ids", "impl": "ours"}
 
 
+# ---------------------------------------------------------------------------------------------- Puledra beside Phi-MoE
+
+def puledra_config(width, heads, dim, rot, vdim, kv_rank, ff, experts, top, groups, keep, layers, vocab, share_every=0):
+    """A Puledra configuration of ``layers`` equal layers (every ``share_every``-th one reads the latent of the
+    layer before it, 0: none does)."""
+    out = []
+    for i in range(layers):
+        m = {"heads": heads, "dim": dim, "rot_dim": rot, "vdim": vdim, "kv_rank": kv_rank,
+             "rot": {"base": 10000.0, "dims": rot}, "scale": (dim + rot) ** -0.5}
+        if share_every and i % share_every == share_every - 1:
+            m["kv_from"] = i - 1
+        out.append({"type": "latent_attention", "mixer": m,
+                    "mlp": {"kind": "moe", "expert": {"ff": ff},
+                            "router": {"experts": experts, "top": top, "groups": {"count": groups, "keep": keep}, "scale": 1.0}}})
+    return {"architecture": "Puledra", "vocab": vocab, "width": width, "norm": {"eps": 1e-5},
+            "embedding": {"scale": 1.0, "bigram": {"buckets": 65521, "mul_prev": 31337, "mul_cur": 7919}}, "layers": out}
+
+
+# layer sizes that resemble real models of this kind, and the Phi-MoE layer of equal width, head count, head size
+# and active expert parameters that each is put beside
+PULEDRA_SIZES = {
+    "2048x16": dict(width=2048, heads=16, dim=128, rot=64, vdim=128, kv_rank=512, ff=1408, experts=64, top=6, groups=8, keep=3,
+                    phi=dict(hidden_size=2048, num_attention_heads=16, num_key_value_heads=4, head_dim=128,
+                             intermediate_size=4224, num_local_experts=16)),
+    "4096x32": dict(width=4096, heads=32, dim=128, rot=64, vdim=128, kv_rank=512, ff=960, experts=16, top=2, groups=1, keep=1,
+                    phi=dict(hidden_size=4096, num_attention_heads=32, num_key_value_heads=8, head_dim=128,
+                             intermediate_size=960, num_local_experts=16)),
+}
+
+
+def run_design_pair(args, pk, rng):
+    """Prefill and decode of Puledra at layer sizes that resemble real models, beside Phi-MoE at equal width, heads
+    and active expert parameters: tokens/s, and for the attention kernels of both the time a layer and the
+    fraction of the measured peak (decode: cache bytes over the copy bandwidth; prefill: flops over the sustained
+    library product rate)."""
+    import torch
+    layers = args.layers or 8
+    vocab = args.vocab or 32064
+    batch, ctx = args.batch, args.prompt_tokens
+    out = {"design": "Puledra", "beside": "PhimoeForCausalLM", "layers": layers, "batch": batch, "prompt_tokens": ctx,
+           "dtype": "bf16", "data": "synthetic: seeded random weights, uniform-random token ids",
+           "peaks": {k: pk[k] for k in ("hbm_gbs", "bf16_tflops_sustained", "source")}, "sizes": {}}
+    for name, sz in PULEDRA_SIZES.items():
+        if args.design_sizes and name not in args.design_sizes:
+            continue
+        phi = sz["phi"]
+        cfgs = {"puledra": puledra_config(**{k: v for k, v in sz.items() if k != "phi"}, layers=layers, vocab=vocab),
+                "phimoe": mini_config(layers, None, {**phi, "vocab_size": vocab})}
+        row = {}
+        for which, cfg in cfgs.items():
+            cfg.setdefault("vocab_size", cfg.get("vocab"))
+            model = build_model(cfg, max(batch, 1), ctx + 256)
+            pre_ms = run_prefill(model, cfg, ctx, reps=3, warmup=3, rng=rng)
+            dec = run_decode(model, cfg, batch, ctx, args.steps, max(args.warmup, 3), rng, count_experts=False)
+            pre_t, dec_t, _ = profile_tables(model, cfg, batch, ctx, rng)
+            kv = ctx + 2
+            if which == "puledra":
+                m = model.layers[0].parts["mixer"]
+                att_bytes = batch * kv * m.row_w * 2
+                att_flops = sum(2 * m.H * (m.Dk + m.C) * k for k in range(1, ctx + 1))
+                names = ("flint_latent_attention", "flint_head_products", "flint_latent_prepare", "flint_router_topk")
+            else:
+                nq, nkv, hd = phi["num_attention_heads"], phi["num_key_value_heads"], phi["head_dim"]
+                att_bytes = batch * kv * nkv * hd * 2 * 2
+                att_flops = sum(4 * nq * hd * k for k in range(1, ctx + 1))
+                names = ("flint_attention", "flint_rope_kv_write", "flint_row_norm")
+            kern = {}
+            for kind, table in (("prefill", pre_t), ("decode", dec_t)):
+                for kname, (n, ms) in sorted(table.items()):
+                    if not kname.startswith(names):
+                        continue
+                    e = {"launches": n, "us_per_layer": round(ms * 1000.0 / layers, 2)}
+                    if "attention" in kname and "prepare" not in kname:
+                        if kind == "decode":
+                            e["frac_of_copy_bandwidth"] = round(att_bytes / (ms / layers * 1e-3) / 1e9 / pk["hbm_gbs"], 4)
+                        else:
+                            e["frac_of_sustained_product_rate"] = round(att_flops / (ms / layers * 1e-3) / (pk["bf16_tflops_sustained"] * 1e12), 4)
+                    kern[f"{kind}: {kname}"] = e
+            row[which] = {"prefill_tok_s": round(ctx * 1000.0 / pre_ms, 1), "prefill_ms": round(pre_ms, 3),
+                          "decode_tok_s": round(dec["tok_s"], 1), "decode_ms_per_step": round(dec["ms"], 4),
+                          "decode_launches": dec["launches"], "weight_gb": round(model.weight_bytes() / 1e9, 2), "kernels": kern}
+            del model
+            torch.cuda.empty_cache()
+        out["sizes"][name] = row
+    return out
+
+
 def config_of(cfg, batch, prompt_tokens, ctx, pk):
     """Every size of a run, flat."""
     mini = all(cfg[k] == MINI[k] for k in MINI if k != "num_hidden_layers")
@@ -659,6 +746,10 @@ def main():
     ap.add_argument("--sweep", action="store_true",
                     help="instead of the default run: decode at batch 1 and 8 with contexts of 16,384 and 65,536 tokens, "
                          "batch 1 with 131,008, and batch 128 and 256 with 2,048, each with its roofline fraction")
+    ap.add_argument("--design", choices=["puledra"], default=None,
+                    help="prefill and decode of this design at layer sizes that resemble real models, beside Phi-MoE at "
+                         "equal width, heads and active expert parameters, with the attention kernels' shares of the peaks")
+    ap.add_argument("--design-sizes", nargs="+", default=None, help="which of the design's size points to run")
     ap.add_argument("--profile", action="store_true",
                     help="print per-kernel device times of one prefill and one decode step to stderr and exit")
     args = ap.parse_args()
@@ -687,6 +778,9 @@ def main():
     rng = random.Random(0)
     if args.tiny:
         print(json.dumps(run_tiny(args.tiny)))
+        return 0
+    if args.design:
+        print(json.dumps(run_design_pair(args, pk, rng)))
         return 0
     if args.sweep:
         print(json.dumps(run_sweep(cfg, pk, rng, max(8, args.steps // 4), warmup)))

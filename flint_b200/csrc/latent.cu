@@ -247,7 +247,8 @@ latent_attention_kernel(const TQ* __restrict__ qa, const TC* __restrict__ k_cach
 // warps of a row tile agree on the new maximum and sum through shared memory, the probabilities go to
 // shared memory as bfloat16, and the warp then adds P V for ITS quarter of the latent dims (V is the start
 // of the key rows already in shared memory, through ldmatrix.trans): the output accumulator of 16 rows by
-// up to 128 dims stays in registers.  Causal and window masks are per row.  With n_splits > 1 the key
+// up to 128 dims stays in registers.  Tiles arrive by asynchronous copies into two buffers: the next tile is on
+// its way while this one is worked.  Causal and window masks are per row.  With n_splits > 1 the key
 // range of a run is cut and the pieces are merged by attention_combine_kernel.
 constexpr int TM = 32;        // query rows per block
 constexpr int KT = 64;        // keys per tile
@@ -269,11 +270,12 @@ latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ qa, const __nv_bfl
   const int QS = Dkp + 8;                                        // row stride of Qs and Ks (elements): odd in 16-byte units
   constexpr int PS = KT + 8;
   __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);
-  __nv_bfloat16* Ks = Qs + (size_t)TM * QS;
-  __nv_bfloat16* Ps = Ks + (size_t)KT * QS + 512;                // slack: the value phase may read columns past a row's end
+  __nv_bfloat16* Kb = Qs + (size_t)TM * QS;                      // two buffers of KT rows, filled by asynchronous copies
+  const size_t kbuf = (size_t)KT * QS;
+  __nv_bfloat16* Ps = Kb + 2 * kbuf + 512;                       // slack: the value phase may read columns past a row's end
   float* redm = reinterpret_cast<float*>(Ps + TM * PS);          // [TM][4]
   float* reds = redm + TM * 4;                                   // [TM][4]
-  long long* krow = reinterpret_cast<long long*>(reds + TM * 4); // [KT] cache row of each key of the tile, or -1
+  int* kval = reinterpret_cast<int*>(reds + TM * 4);             // [2][KT]: whether each key of a buffered tile has a page
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int wm = warp >> 2, wk = warp & 3;
   const int t_first = blockIdx.x * nt, h0 = blockIdx.y * nh, split = blockIdx.z;
@@ -293,40 +295,64 @@ latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ qa, const __nv_bfl
     const int hi = min(p_b + 1, lo + split_keys);
     const int* bt = block_table + (size_t)s * max_pages;
     // the run's query rows, zero beyond the row's width and beyond the run
-    for (int e = tid; e < TM * Dkp; e += TC_THREADS) {
-      const int r = e / Dkp, d = e - r * Dkp;
-      __nv_bfloat16 v = __float2bfloat16_rn(0.f);
-      if (r < n_rows && d < Dk) {
-        const int tok = t_first + ta + r / nhh, h = h0 + r % nhh;
-        v = qa[((size_t)tok * H + h) * Dk + d];
+    if ((Dk & 7) == 0) {
+      for (int c = tid; c < TM * cpr; c += TC_THREADS) {
+        const int r = c / cpr, cu = c - r * cpr;
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (r < n_rows && cu * 8 < Dk) {
+          const int tok = t_first + ta + r / nhh, h = h0 + r % nhh;
+          v = *reinterpret_cast<const uint4*>(qa + ((size_t)tok * H + h) * Dk + cu * 8);
+        }
+        *reinterpret_cast<uint4*>(Qs + (size_t)r * QS + cu * 8) = v;
       }
-      Qs[(size_t)r * QS + d] = v;
+    } else {
+      for (int e = tid; e < TM * Dkp; e += TC_THREADS) {
+        const int r = e / Dkp, d = e - r * Dkp;
+        __nv_bfloat16 v = __float2bfloat16_rn(0.f);
+        if (r < n_rows && d < Dk) {
+          const int tok = t_first + ta + r / nhh, h = h0 + r % nhh;
+          v = qa[((size_t)tok * H + h) * Dk + d];
+        }
+        Qs[(size_t)r * QS + d] = v;
+      }
     }
+    // a tile's rows are fetched by asynchronous 16-byte copies (zeros where there is no key): thread t brings
+    // every fourth unit of key t / 4, so it looks the key's page up once
+    auto fetch = [&](int j0, int buf) {
+      const int jj = tid >> 2, j = j0 + jj;
+      long long row = -1;
+      if (j < hi) {
+        const int page = bt[j / page_size];
+        if (page >= 0) row = (long long)page * page_size + (j % page_size);
+      }
+      if ((tid & 3) == 0) kval[buf * KT + jj] = row >= 0;
+      const __nv_bfloat16* src = k_cache + (row >= 0 ? row * row_w : 0);
+      const uint32_t dst = smem_addr(Kb + buf * kbuf + (size_t)jj * QS);
+      for (int cu = tid & 3; cu < cpr; cu += 4) {
+        const bool live = row >= 0 && cu * 8 < row_w;
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst + cu * 16), "l"(live ? src + cu * 8 : k_cache),
+                     "r"(live ? 16 : 0) : "memory");
+      }
+      asm volatile("cp.async.commit_group;" ::: "memory");
+    };
     const int p_lo = p_a + r_lo / nhh, p_hi = p_a + r_hi / nhh;   // positions of this lane's rows (if they are in the run)
     float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.f, l_hi = 0.f;
     float o[NTW][4];
 #pragma unroll
     for (int i = 0; i < NTW; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
 
-    for (int j0 = lo; j0 < hi; j0 += KT) {
-      if (tid < KT) {
-        const int j = j0 + tid;
-        long long row = -1;
-        if (j < hi) {
-          const int page = bt[j / page_size];
-          if (page >= 0) row = (long long)page * page_size + (j % page_size);
-        }
-        krow[tid] = row;
+    if (lo < hi) fetch(lo, 0);
+    int buf = 0;
+    for (int j0 = lo; j0 < hi; j0 += KT, buf ^= 1) {
+      if (j0 + KT < hi) {
+        fetch(j0 + KT, buf ^ 1);                                   // that buffer's last readers passed the barrier below
+        asm volatile("cp.async.wait_group 1;" ::: "memory");
+      } else {
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
       }
       __syncthreads();
-      for (int c = tid; c < KT * cpr; c += TC_THREADS) {
-        const int jj = c / cpr, cu = c - jj * cpr;
-        const long long row = krow[jj];
-        uint4 v = make_uint4(0u, 0u, 0u, 0u);
-        if (row >= 0 && cu * 8 < row_w) v = *reinterpret_cast<const uint4*>(k_cache + row * row_w + cu * 8);
-        *reinterpret_cast<uint4*>(Ks + (size_t)jj * QS + cu * 8) = v;
-      }
-      __syncthreads();
+      const __nv_bfloat16* Ks = Kb + buf * kbuf;
+      const int* kv_ok = kval + buf * KT;
       // ---- scores of 16 rows x 16 keys
       float sc[2][4];
 #pragma unroll
@@ -349,7 +375,7 @@ latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ qa, const __nv_bfl
         for (int i = 0; i < 4; ++i) {
           const int j = j0 + wk * 16 + n * 8 + 2 * (lane & 3) + (i & 1);
           const int r = i < 2 ? r_lo : r_hi, p = i < 2 ? p_lo : p_hi;
-          const bool seen = r < n_rows && j < hi && j <= p && (window <= 0 || j > p - window) && krow[j - j0] >= 0;
+          const bool seen = r < n_rows && j < hi && j <= p && (window <= 0 || j > p - window) && kv_ok[j - j0];
           sc[n][i] = seen ? sc[n][i] * scale : -INFINITY;
           if (i < 2) mx_lo = fmaxf(mx_lo, sc[n][i]); else mx_hi = fmaxf(mx_hi, sc[n][i]);
         }
@@ -443,6 +469,70 @@ latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ qa, const __nv_bfl
     ta = tb;
   }
 }
+// ---------------------------------------------------------------------------------------------
+// A small product per head, all heads in one launch: out[t, h, :] = W[h] x[t, h, :] (bfloat16 in and out,
+// float32 sums).  x and out may be views into wider rows (strides in elements).  Block (64 tokens, 64 outputs,
+// head): four warps of 16 tokens each, operands staged in shared memory 32 columns at a time.
+constexpr int HP_M = 64, HP_N = 64, HP_K = 32, HP_S = HP_K + 8;
+
+__global__ void __launch_bounds__(128)
+head_products_kernel(const __nv_bfloat16* __restrict__ x, long long sx_t, long long sx_h,
+                     const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ out, long long so_t,
+                     long long so_h, int T, int N, int K) {
+  using flint_attn::ldsm4;
+  using flint_attn::mma16816;
+  __shared__ __align__(16) __nv_bfloat16 As[HP_M * HP_S];
+  __shared__ __align__(16) __nv_bfloat16 Bs[HP_N * HP_S];
+  pdl_launch();
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int t0 = blockIdx.x * HP_M, n0 = blockIdx.y * HP_N, h = blockIdx.z;
+  const __nv_bfloat16* xh = x + (size_t)h * sx_h;
+  const __nv_bfloat16* wh = w + (size_t)h * N * K;
+  float acc[HP_N / 8][4];
+#pragma unroll
+  for (int i = 0; i < HP_N / 8; ++i) { acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f; }
+  pdl_wait();
+  for (int k0 = 0; k0 < K; k0 += HP_K) {
+    for (int c = tid; c < (HP_M + HP_N) * (HP_K / 8); c += 128) {
+      const int r = c / (HP_K / 8), cu = c % (HP_K / 8), k = k0 + cu * 8;
+      uint4 v = make_uint4(0u, 0u, 0u, 0u);
+      if (r < HP_M) {
+        if (t0 + r < T && k < K) v = *reinterpret_cast<const uint4*>(xh + (size_t)(t0 + r) * sx_t + k);
+        *reinterpret_cast<uint4*>(As + r * HP_S + cu * 8) = v;
+      } else {
+        const int n = r - HP_M;
+        if (n0 + n < N && k < K) v = *reinterpret_cast<const uint4*>(wh + (size_t)(n0 + n) * K + k);
+        *reinterpret_cast<uint4*>(Bs + n * HP_S + cu * 8) = v;
+      }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < HP_K; kk += 16) {
+      uint32_t a0, a1, a2, a3;
+      ldsm4(smem_addr(As + (warp * 16 + (lane & 15)) * HP_S + kk + (lane >> 4) * 8), a0, a1, a2, a3);
+#pragma unroll
+      for (int nb = 0; nb < HP_N / 8; nb += 2) {
+        uint32_t b0, b1, b2, b3;
+        ldsm4(smem_addr(Bs + (nb * 8 + ((lane >> 4) << 3) + (lane & 7)) * HP_S + kk + ((lane >> 3) & 1) * 8), b0, b1, b2, b3);
+        mma16816(acc[nb], a0, a1, a2, a3, b0, b1);
+        mma16816(acc[nb + 1], a0, a1, a2, a3, b2, b3);
+      }
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    const int t = t0 + warp * 16 + (lane >> 2) + 8 * half;
+    if (t >= T) continue;
+    __nv_bfloat16* dst = out + (size_t)t * so_t + (size_t)h * so_h;
+#pragma unroll
+    for (int nb = 0; nb < HP_N / 8; ++nb) {
+      const int n = n0 + nb * 8 + 2 * (lane & 3);
+      if (n < N) dst[n] = __float2bfloat16_rn(acc[nb][2 * half]);
+      if (n + 1 < N) dst[n + 1] = __float2bfloat16_rn(acc[nb][2 * half + 1]);
+    }
+  }
+}
 }  // namespace
 
 // proj [S, T, W] float32 partial sums of [q | latent] (W = H (D + R) + (write_kv ? C + R : 0)); q_plain
@@ -522,8 +612,8 @@ extern "C" int flint_latent_attention_mma(const void* qa, const void* k_cache, c
   if (((uintptr_t)k_cache & 15) != 0) return fail("latent_attention: the cache must be 16-byte aligned");
   const int Dkp = (row_w + 15) / 16 * 16;
   const int QS = Dkp + 8;
-  const size_t smem = ((size_t)TM * QS + (size_t)KT * QS + 512 + (size_t)TM * (KT + 8)) * sizeof(__nv_bfloat16) +
-                      (size_t)TM * 8 * sizeof(float) + KT * sizeof(long long);
+  const size_t smem = ((size_t)TM * QS + 2 * (size_t)KT * QS + 512 + (size_t)TM * (KT + 8)) * sizeof(__nv_bfloat16) +
+                      (size_t)TM * 8 * sizeof(float) + 2 * KT * sizeof(int);
   if (smem > 220 * 1024) return fail("latent_attention: rows of %d numbers are too wide", row_w);
   dim3 grid((T + nt - 1) / nt, (H + nh - 1) / nh, n_splits);
   if (grid.y > 65535 || grid.z > 65535) return fail("latent_attention: too many head chunks or splits");
@@ -546,6 +636,20 @@ extern "C" int flint_latent_attention_mma(const void* qa, const void* k_cache, c
   flint_attn::attention_combine_kernel<__nv_bfloat16><<<(unsigned)((long long)T * H), threads, 0, stream>>>(
       scratch, (__nv_bfloat16*)out, C, n_splits, H, nullptr);
   return check_launch("latent_attention (merge)");
+}
+
+// out[t, h, :] = W[h] x[t, h, :] for all heads: x [T, H, K] and out [T, H, N] bfloat16 with strides (elements) per
+// token and per head, w [H, N, K] bfloat16.  K and the strides of x must be multiples of 8, x and w 16-byte aligned.
+extern "C" int flint_head_products(const void* x, long long sx_t, long long sx_h, const void* w, void* out,
+                                   long long so_t, long long so_h, int T, int H, int N, int K, cudaStream_t stream) {
+  if (T <= 0 || H <= 0 || N <= 0) return 0;
+  if (K <= 0 || (K & 7) || (sx_t & 7) || (sx_h & 7) || ((uintptr_t)x & 15) || ((uintptr_t)w & 15))
+    return fail("head_products: K=%d and the strides of x must be multiples of 8, x and w 16-byte aligned", K);
+  if (H > 65535 || (N + HP_N - 1) / HP_N > 65535) return fail("head_products: too many heads or outputs");
+  dim3 grid((T + HP_M - 1) / HP_M, (N + HP_N - 1) / HP_N, H);
+  launch_pdl(head_products_kernel, grid, dim3(128), 0, stream, (const __nv_bfloat16*)x, sx_t, sx_h,
+             (const __nv_bfloat16*)w, (__nv_bfloat16*)out, so_t, so_h, T, N, K);
+  return check_launch("head_products");
 }
 
 extern "C" const char* flint_latent_last_error() { return g_error; }

@@ -136,7 +136,7 @@ router_sparsemixer_kernel(const float* __restrict__ x, const TW* __restrict__ wr
 // Softmax router with a choice limited to groups: s = softmax(logits); the experts form n_groups equal groups of
 // neighbours, a group scores as its best member, only members of the `keep` best groups may be chosen, and the
 // `top` best of those are (lowest index first among equals).  Gates: s_e / (sum of the chosen s + 1e-20) * scale.
-// One thread per token does the selection; everything is float32.
+// One warp per token does the selection (a lane holds every 32nd expert); everything is float32.
 constexpr int MAX_TOP = 16;
 template <typename TW>
 __global__ void __launch_bounds__(ROUTER_WARPS * 32)
@@ -151,50 +151,92 @@ router_topk_kernel(const float* __restrict__ x, const TW* __restrict__ wr, int t
   const int t0 = blockIdx.x * TT;
   const int nt = min(TT, T - t0);
   block_router_logits<TW>(x, wr, xs, s_all, t0, nt, H, E, vec_ok);
-  if (threadIdx.x >= nt) return;
-  const int t = t0 + threadIdx.x;
-  float* s = s_all + threadIdx.x * E;
-  if (logits_out)
-    for (int e = 0; e < E; ++e) logits_out[(size_t)t * E + e] = s[e];
+  // one warp per token: lane l holds experts l, l + 32, ...
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (warp >= nt) return;
+  const int t = t0 + warp;
+  float* s = s_all + warp * E;
+  constexpr int EPL = MAX_E / 32;
+  float v[EPL];
   float m = -INFINITY;
-  for (int e = 0; e < E; ++e) m = fmaxf(m, s[e]);
-  float denom = 0.f;
-  for (int e = 0; e < E; ++e) denom += expf(s[e] - m);
-  for (int e = 0; e < E; ++e) s[e] = expf(s[e] - m) / denom;
-  // the groups that stay: bit g of `kept`
-  const int per = E / n_groups;
-  unsigned long long kept = 0ull;
-  if (keep >= n_groups) kept = ~0ull;
-  else
-    for (int r = 0; r < keep; ++r) {
-      float best = -1.f;
-      int bg = 0;
-      for (int g = 0; g < n_groups; ++g) {
-        if (kept >> g & 1ull) continue;
-        float gs = 0.f;
-        for (int e = g * per; e < (g + 1) * per; ++e) gs = fmaxf(gs, s[e]);
-        if (gs > best) { best = gs; bg = g; }
-      }
-      kept |= 1ull << bg;
-    }
-  int sel[MAX_TOP];
-  float val[MAX_TOP], sum = 0.f;
-  for (int r = 0; r < top; ++r) {
-    float best = -1.f;
-    int be = 0;
-    for (int e = 0; e < E; ++e) {
-      if (!(kept >> (e / per) & 1ull)) continue;
-      bool taken = false;
-      for (int q = 0; q < r; ++q) taken |= sel[q] == e;
-      if (!taken && s[e] > best) { best = s[e]; be = e; }
-    }
-    sel[r] = be;
-    val[r] = best;
-    sum += best;
+#pragma unroll
+  for (int i = 0; i < EPL; ++i) {
+    const int e = lane + 32 * i;
+    v[i] = e < E ? s[e] : -INFINITY;
+    if (logits_out && e < E) logits_out[(size_t)t * E + e] = v[i];
+    m = fmaxf(m, v[i]);
   }
+  m = warp_max(m);
+  float denom = 0.f;
+#pragma unroll
+  for (int i = 0; i < EPL; ++i) {
+    v[i] = lane + 32 * i < E ? expf(v[i] - m) : 0.f;
+    denom += v[i];
+  }
+  denom = warp_sum(denom);
+  __syncwarp();
+#pragma unroll
+  for (int i = 0; i < EPL; ++i) {
+    const int e = lane + 32 * i;
+    v[i] = e < E ? v[i] / denom : -1.f;          // scores; -1 marks what cannot be chosen
+    if (e < E) s[e] = v[i];
+  }
+  __syncwarp();
+  // the best of (value, index) pairs over the warp: the larger value, the lower index among equals
+  auto best_of_warp = [&](float& val, int& idx) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, val, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+      if (ov > val || (ov == val && oi < idx)) { val = ov; idx = oi; }
+    }
+  };
+  const int per = E / n_groups;
+  unsigned long long kept = ~0ull;
+  if (keep < n_groups) {
+    float gs[2];                                  // the scores of groups lane and lane + 32
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+      const int g = lane + 32 * k;
+      gs[k] = -1.f;
+      if (g < n_groups)
+        for (int e = g * per; e < (g + 1) * per; ++e) gs[k] = fmaxf(gs[k], s[e]);
+    }
+    kept = 0ull;
+    for (int r = 0; r < keep; ++r) {
+      float val = gs[0];
+      int idx = lane;
+      if (gs[1] > val) { val = gs[1]; idx = lane + 32; }
+      best_of_warp(val, idx);
+      kept |= 1ull << idx;
+      if ((idx & 31) == lane) gs[idx >> 5] = -2.f;
+    }
+#pragma unroll
+    for (int i = 0; i < EPL; ++i) {
+      const int e = lane + 32 * i;
+      if (e < E && !(kept >> (e / per) & 1ull)) v[i] = -1.f;
+    }
+  }
+  float my_val = 0.f, sum = 0.f;
+  int my_sel = 0;
   for (int r = 0; r < top; ++r) {
-    expert_ids[(size_t)t * top + r] = sel[r];
-    gates[(size_t)t * top + r] = val[r] / (sum + 1e-20f) * out_scale;
+    float val = -1.f;
+    int idx = 0x7fffffff;
+#pragma unroll
+    for (int i = 0; i < EPL; ++i)
+      if (v[i] > val) { val = v[i]; idx = lane + 32 * i; }
+    best_of_warp(val, idx);
+    if ((idx & 31) == lane) {
+#pragma unroll
+      for (int i = 0; i < EPL; ++i)
+        if (i == (idx >> 5)) v[i] = -1.f;
+    }
+    if (lane == r) { my_val = val; my_sel = idx; }
+    sum += val;
+  }
+  if (lane < top) {
+    expert_ids[(size_t)t * top + lane] = my_sel;
+    gates[(size_t)t * top + lane] = my_val / (sum + 1e-20f) * out_scale;
   }
 }
 

@@ -711,6 +711,12 @@ class CudaOps:
             raise KernelError(f"head_products: shapes x{tuple(x.shape)} w{tuple(w.shape)} out{tuple(out.shape)} do not match")
         if x.stride(2) != 1 or out.stride(2) != 1:
             raise KernelError("head_products: the last axis must be contiguous")
+        if (x.dtype == w.dtype == out.dtype == torch.bfloat16 and K % 8 == 0 and x.stride(0) % 8 == 0 and x.stride(1) % 8 == 0
+                and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0):
+            # all heads in one launch on the tensor cores
+            return self._run("latent", "flint_head_products", _ptr(x), c_longlong(x.stride(0)), c_longlong(x.stride(1)),
+                             _ptr(w), _ptr(out), c_longlong(out.stride(0)), c_longlong(out.stride(1)), c_int(T), c_int(H),
+                             c_int(N), c_int(K))
         for h in range(H):
             self.gemm(x[:, h, :], w[h], out[:, h, :])
 
@@ -773,7 +779,7 @@ class CudaOps:
         if qa.shape[1] != H or tuple(out.shape) != (T, H, C) or tuple(k.shape[1:]) != (1, P, row_w) or row_w < Dk:
             raise KernelError("latent_attention: shapes do not match")
         span = min(step.max_kv_len, window) if window else step.max_kv_len
-        mma_ok = qa.dtype == torch.bfloat16 and k.dtype == torch.bfloat16 and rows is None and C <= 512 and row_w <= 1024
+        mma_ok = qa.dtype == torch.bfloat16 and k.dtype == torch.bfloat16 and rows is None and C <= 512 and row_w <= 640
         if kernel is None:
             kernel = "mma" if mma_ok else "simt"
         if kernel == "mma":
