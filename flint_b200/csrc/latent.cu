@@ -278,7 +278,8 @@ latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ qa, const __nv_bfl
   int* kval = reinterpret_cast<int*>(reds + TM * 4);             // [2][KT]: whether each key of a buffered tile has a page
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int wm = warp >> 2, wk = warp & 3;
-  const int t_first = blockIdx.x * nt, h0 = blockIdx.y * nh, split = blockIdx.z;
+  // the last tokens first: in a prompt's portion they see the most keys, and the short blocks fill in behind them
+  const int t_first = (gridDim.x - 1 - blockIdx.x) * nt, h0 = blockIdx.y * nh, split = blockIdx.z;
   const int ntok = min(nt, T - t_first), nhh = min(nh, H - h0);
   const int r_lo = wm * 16 + (lane >> 2), r_hi = r_lo + 8;       // the two query rows of this lane's fragments
   const int cpr = Dkp / 8;                                       // 16-byte units per staged row
@@ -318,13 +319,17 @@ latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ qa, const __nv_bfl
     }
     // a tile's rows are fetched by asynchronous 16-byte copies (zeros where there is no key): thread t brings
     // every fourth unit of key t / 4, so it looks the key's page up once
+    auto row_of_key = [&](int j0) {            // the cache row of this thread's key of the tile at j0, or -1
+      const int j = j0 + (tid >> 2);
+      if (j >= hi) return -1ll;
+      const int page = bt[j / page_size];
+      return page >= 0 ? (long long)page * page_size + (j % page_size) : -1ll;
+    };
+    long long next_row = lo < hi ? row_of_key(lo) : -1ll;    // looked up a tile ahead of its use
     auto fetch = [&](int j0, int buf) {
-      const int jj = tid >> 2, j = j0 + jj;
-      long long row = -1;
-      if (j < hi) {
-        const int page = bt[j / page_size];
-        if (page >= 0) row = (long long)page * page_size + (j % page_size);
-      }
+      const int jj = tid >> 2;
+      const long long row = next_row;
+      next_row = row_of_key(j0 + KT);
       if ((tid & 3) == 0) kval[buf * KT + jj] = row >= 0;
       const __nv_bfloat16* src = k_cache + (row >= 0 ? row * row_w : 0);
       const uint32_t dst = smem_addr(Kb + buf * kbuf + (size_t)jj * QS);
@@ -354,19 +359,34 @@ latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ qa, const __nv_bfl
       const __nv_bfloat16* Ks = Kb + buf * kbuf;
       const int* kv_ok = kval + buf * KT;
       // ---- scores of 16 rows x 16 keys
-      float sc[2][4];
+      float sc[2][4], sd[2][4];       // even and odd steps of the dims add into accumulators of their own: two chains
 #pragma unroll
-      for (int n = 0; n < 2; ++n) { sc[n][0] = sc[n][1] = sc[n][2] = sc[n][3] = 0.f; }
+      for (int n = 0; n < 2; ++n) { sc[n][0] = sc[n][1] = sc[n][2] = sc[n][3] = 0.f; sd[n][0] = sd[n][1] = sd[n][2] = sd[n][3] = 0.f; }
       {
         const uint32_t qaddr = smem_addr(Qs + (size_t)(wm * 16 + (lane & 15)) * QS + (lane >> 4) * 8);
         const uint32_t kaddr = smem_addr(Ks + (size_t)(wk * 16 + ((lane >> 4) << 3) + (lane & 7)) * QS + ((lane >> 3) & 1) * 8);
-        for (int kk = 0; kk < Dkp; kk += 16) {
+        int kk = 0;
+#pragma unroll 2
+        for (; kk + 32 <= Dkp; kk += 32) {
+          uint32_t a0, a1, a2, a3, b0, b1, b2, b3, c0, c1, c2, c3, d0, d1, d2, d3;
+          ldsm4(qaddr + kk * 2, a0, a1, a2, a3);
+          ldsm4(kaddr + kk * 2, b0, b1, b2, b3);
+          ldsm4(qaddr + kk * 2 + 32, c0, c1, c2, c3);
+          ldsm4(kaddr + kk * 2 + 32, d0, d1, d2, d3);
+          mma16816(sc[0], a0, a1, a2, a3, b0, b1);
+          mma16816(sc[1], a0, a1, a2, a3, b2, b3);
+          mma16816(sd[0], c0, c1, c2, c3, d0, d1);
+          mma16816(sd[1], c0, c1, c2, c3, d2, d3);
+        }
+        if (kk < Dkp) {
           uint32_t a0, a1, a2, a3, b0, b1, b2, b3;
           ldsm4(qaddr + kk * 2, a0, a1, a2, a3);
           ldsm4(kaddr + kk * 2, b0, b1, b2, b3);
           mma16816(sc[0], a0, a1, a2, a3, b0, b1);
           mma16816(sc[1], a0, a1, a2, a3, b2, b3);
         }
+#pragma unroll
+        for (int n = 0; n < 2; ++n) { sc[n][0] += sd[n][0]; sc[n][1] += sd[n][1]; sc[n][2] += sd[n][2]; sc[n][3] += sd[n][3]; }
       }
       float mx_lo = -INFINITY, mx_hi = -INFINITY;
 #pragma unroll
@@ -414,8 +434,10 @@ latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ qa, const __nv_bfl
       m_lo = mn_lo;
       m_hi = mn_hi;
       // ---- O += P V for this warp's dims [32 NTW wk / 4 ...): 16 rows x 8 NTW dims
+      if (__any_sync(0xffffffffu, al_lo != 1.f || al_hi != 1.f)) {     // a maximum moved: rescale what was added so far
 #pragma unroll
-      for (int i = 0; i < NTW; ++i) { o[i][0] *= al_lo; o[i][1] *= al_lo; o[i][2] *= al_hi; o[i][3] *= al_hi; }
+        for (int i = 0; i < NTW; ++i) { o[i][0] *= al_lo; o[i][1] *= al_lo; o[i][2] *= al_hi; o[i][3] *= al_hi; }
+      }
       {
         const uint32_t paddr = smem_addr(Ps + (wm * 16 + (lane & 15)) * PS + (lane >> 4) * 8);
         const uint32_t vaddr = smem_addr(Ks + (size_t)((((lane >> 3) & 1) << 3) + (lane & 7)) * QS + (lane >> 4) * 8);
