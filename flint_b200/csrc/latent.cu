@@ -255,6 +255,11 @@ constexpr int KT = 64;        // keys per tile
 constexpr int TC_THREADS = 256;
 
 __device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ float ex2(float x) {          // 2^x; 2^-inf = 0
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 
 template <int NTW>            // blocks of 8 latent dims per warp in the value phase: latent size <= 32 NTW
 __global__ void __launch_bounds__(TC_THREADS)
@@ -282,7 +287,15 @@ latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ qa, const __nv_bfl
   const int t_first = (gridDim.x - 1 - blockIdx.x) * nt, h0 = blockIdx.y * nh, split = blockIdx.z;
   const int ntok = min(nt, T - t_first), nhh = min(nh, H - h0);
   const int r_lo = wm * 16 + (lane >> 2), r_hi = r_lo + 8;       // the two query rows of this lane's fragments
+  const float scale2 = scale * 1.4426950408889634f;              // scores are kept in units of log 2
   const int cpr = Dkp / 8;                                       // 16-byte units per staged row
+  const int row_units = row_w / 8;                               // of which the cached row fills so many
+  pdl_launch();
+  // a staged row may be one unit wider than the cached row: that unit stays zero in both buffers
+  if (row_units < cpr)
+    for (int r = tid; r < 2 * KT; r += TC_THREADS)
+      *reinterpret_cast<uint4*>(Kb + (size_t)r * QS + row_units * 8) = make_uint4(0u, 0u, 0u, 0u);
+  pdl_wait();
 
   int ta = 0;
   while (ta < ntok) {
@@ -331,13 +344,11 @@ latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ qa, const __nv_bfl
       const long long row = next_row;
       next_row = row_of_key(j0 + KT);
       if ((tid & 3) == 0) kval[buf * KT + jj] = row >= 0;
-      const __nv_bfloat16* src = k_cache + (row >= 0 ? row * row_w : 0);
-      const uint32_t dst = smem_addr(Kb + buf * kbuf + (size_t)jj * QS);
-      for (int cu = tid & 3; cu < cpr; cu += 4) {
-        const bool live = row >= 0 && cu * 8 < row_w;
-        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst + cu * 16), "l"(live ? src + cu * 8 : k_cache),
-                     "r"(live ? 16 : 0) : "memory");
-      }
+      const __nv_bfloat16* src = k_cache + (row >= 0 ? row * row_w : 0) + (tid & 3) * 8;
+      uint32_t dst = smem_addr(Kb + buf * kbuf + (size_t)jj * QS) + (tid & 3) * 16;
+      const int size = row >= 0 ? 16 : 0;                        // no key: the units are filled with zeros
+      for (int cu = tid & 3; cu < row_units; cu += 4, src += 32, dst += 64)
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(size) : "memory");
       asm volatile("cp.async.commit_group;" ::: "memory");
     };
     const int p_lo = p_a + r_lo / nhh, p_hi = p_a + r_hi / nhh;   // positions of this lane's rows (if they are in the run)
@@ -388,17 +399,29 @@ latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ qa, const __nv_bfl
 #pragma unroll
         for (int n = 0; n < 2; ++n) { sc[n][0] += sd[n][0]; sc[n][1] += sd[n][1]; sc[n][2] += sd[n][2]; sc[n][3] += sd[n][3]; }
       }
+      // scores in units of log 2 (the scale carries log2 e), so that the exponentials are single instructions; a tile
+      // that every row of the run sees whole needs no masks
       float mx_lo = -INFINITY, mx_hi = -INFINITY;
+      const bool whole = j0 + KT <= hi && j0 + KT - 1 <= p_a && (window <= 0 || j0 > p_b - window) && n_rows == TM;
+      if (whole) {
 #pragma unroll
-      for (int n = 0; n < 2; ++n)
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const int j = j0 + wk * 16 + n * 8 + 2 * (lane & 3) + (i & 1);
-          const int r = i < 2 ? r_lo : r_hi, p = i < 2 ? p_lo : p_hi;
-          const bool seen = r < n_rows && j < hi && j <= p && (window <= 0 || j > p - window) && kv_ok[j - j0];
-          sc[n][i] = seen ? sc[n][i] * scale : -INFINITY;
-          if (i < 2) mx_lo = fmaxf(mx_lo, sc[n][i]); else mx_hi = fmaxf(mx_hi, sc[n][i]);
+        for (int n = 0; n < 2; ++n) {
+          sc[n][0] *= scale2; sc[n][1] *= scale2; sc[n][2] *= scale2; sc[n][3] *= scale2;
+          mx_lo = fmaxf(mx_lo, fmaxf(sc[n][0], sc[n][1]));
+          mx_hi = fmaxf(mx_hi, fmaxf(sc[n][2], sc[n][3]));
         }
+      } else {
+#pragma unroll
+        for (int n = 0; n < 2; ++n)
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const int j = j0 + wk * 16 + n * 8 + 2 * (lane & 3) + (i & 1);
+            const int r = i < 2 ? r_lo : r_hi, p = i < 2 ? p_lo : p_hi;
+            const bool seen = r < n_rows && j < hi && j <= p && (window <= 0 || j > p - window) && kv_ok[j - j0];
+            sc[n][i] = seen ? sc[n][i] * scale2 : -INFINITY;
+            if (i < 2) mx_lo = fmaxf(mx_lo, sc[n][i]); else mx_hi = fmaxf(mx_hi, sc[n][i]);
+          }
+      }
       mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 1));
       mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 2));
       mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1));
@@ -408,15 +431,15 @@ latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ qa, const __nv_bfl
       float mn_lo = m_lo, mn_hi = m_hi;
 #pragma unroll
       for (int w = 0; w < 4; ++w) { mn_lo = fmaxf(mn_lo, redm[r_lo * 4 + w]); mn_hi = fmaxf(mn_hi, redm[r_hi * 4 + w]); }
-      const float al_lo = mn_lo > -INFINITY ? expf(m_lo - mn_lo) : 1.f;      // 0 while m is still -inf
-      const float al_hi = mn_hi > -INFINITY ? expf(m_hi - mn_hi) : 1.f;
+      // a row that has seen no key yet keeps m = -inf; its exponentials are taken against 0 and come out 0
+      const float ref_lo = mn_lo > -INFINITY ? mn_lo : 0.f, ref_hi = mn_hi > -INFINITY ? mn_hi : 0.f;
+      const float al_lo = mn_lo == m_lo ? 1.f : ex2(m_lo - ref_lo);
+      const float al_hi = mn_hi == m_hi ? 1.f : ex2(m_hi - ref_hi);
       float sum_lo = 0.f, sum_hi = 0.f;
 #pragma unroll
       for (int n = 0; n < 2; ++n) {
-        const float p0 = sc[n][0] > -INFINITY ? expf(sc[n][0] - mn_lo) : 0.f;
-        const float p1 = sc[n][1] > -INFINITY ? expf(sc[n][1] - mn_lo) : 0.f;
-        const float p2 = sc[n][2] > -INFINITY ? expf(sc[n][2] - mn_hi) : 0.f;
-        const float p3 = sc[n][3] > -INFINITY ? expf(sc[n][3] - mn_hi) : 0.f;
+        const float p0 = ex2(sc[n][0] - ref_lo), p1 = ex2(sc[n][1] - ref_lo);
+        const float p2 = ex2(sc[n][2] - ref_hi), p3 = ex2(sc[n][3] - ref_hi);
         sum_lo += p0 + p1;
         sum_hi += p2 + p3;
         const int col = wk * 16 + n * 8 + 2 * (lane & 3);
@@ -483,7 +506,7 @@ latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ qa, const __nv_bfl
             if (col < C) dst[col] = o[nb][2 * half];
             if (col + 1 < C) dst[col + 1] = o[nb][2 * half + 1];
           }
-          if (wk == 0 && (lane & 3) == 0) { dst[C] = m; dst[C + 1] = l; }
+          if (wk == 0 && (lane & 3) == 0) { dst[C] = m * 0.6931471805599453f; dst[C + 1] = l; }   // the merge works in natural logarithms
         }
       }
     }
@@ -643,9 +666,9 @@ extern "C" int flint_latent_attention_mma(const void* qa, const void* k_cache, c
   do {                                                                                                                \
     if (smem > 48 * 1024)                                                                                             \
       cudaFuncSetAttribute(latent_attention_mma_kernel<N>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);  \
-    latent_attention_mma_kernel<N><<<grid, TC_THREADS, smem, stream>>>(                                               \
-        (const __nv_bfloat16*)qa, (const __nv_bfloat16*)k_cache, block_table, max_pages, page_size, pos, slot,        \
-        (__nv_bfloat16*)out, scratch, T, H, C, Dk, row_w, Dkp, window, scale, nt, nh, split_keys, n_splits);          \
+    launch_pdl(latent_attention_mma_kernel<N>, grid, dim3(TC_THREADS), smem, stream,                                  \
+               (const __nv_bfloat16*)qa, (const __nv_bfloat16*)k_cache, block_table, max_pages, page_size, pos, slot, \
+               (__nv_bfloat16*)out, scratch, T, H, C, Dk, row_w, Dkp, window, scale, nt, nh, split_keys, n_splits);   \
   } while (0)
   if (C <= 64) LAUNCH(2);
   else if (C <= 128) LAUNCH(4);
@@ -655,8 +678,8 @@ extern "C" int flint_latent_attention_mma(const void* qa, const void* k_cache, c
   int rc = check_launch("latent_attention (tensor cores)");
   if (rc || n_splits == 1) return rc;
   const int threads = C >= 128 ? 128 : 64;
-  flint_attn::attention_combine_kernel<__nv_bfloat16><<<(unsigned)((long long)T * H), threads, 0, stream>>>(
-      scratch, (__nv_bfloat16*)out, C, n_splits, H, nullptr);
+  launch_pdl(flint_attn::attention_combine_kernel<__nv_bfloat16>, dim3((unsigned)((long long)T * H)), dim3(threads), 0,
+             stream, (const float*)scratch, (__nv_bfloat16*)out, C, n_splits, H, (const int*)nullptr);
   return check_launch("latent_attention (merge)");
 }
 
