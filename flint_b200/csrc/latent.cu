@@ -578,6 +578,57 @@ head_products_kernel(const __nv_bfloat16* __restrict__ x, long long sx_t, long l
     }
   }
 }
+// The same for a handful of tokens (decoded tokens): a warp per output (h, n) reads its weight row once, all loads in
+// flight, and forms the dot products with every token's row (staged in shared memory as float32).
+constexpr int HPS_T = 16;        // tokens at most
+__global__ void __launch_bounds__(256)
+head_products_small_kernel(const __nv_bfloat16* __restrict__ x, long long sx_t, long long sx_h,
+                           const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ out, long long so_t,
+                           long long so_h, int T, int N, int K) {
+  extern __shared__ float xs[];                  // [T][K]
+  pdl_launch();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int h = blockIdx.y, n = blockIdx.x * 8 + warp;
+  // the weight row is no kernel's output: its first units are asked for before the wait
+  const __nv_bfloat16* wrow = w + ((size_t)h * N + min(n, N - 1)) * K;
+  uint4 first = make_uint4(0u, 0u, 0u, 0u);
+  if (lane * 8 < K) first = *reinterpret_cast<const uint4*>(wrow + lane * 8);
+  pdl_wait();
+  for (int i = threadIdx.x; i < T * (K / 8); i += 256) {
+    const int t = i / (K / 8), cu = i - t * (K / 8);
+    float f[8];
+    load8<__nv_bfloat16>(x + (size_t)t * sx_t + (size_t)h * sx_h + cu * 8, f);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) xs[t * K + cu * 8 + e] = f[e];
+  }
+  __syncthreads();
+  if (n >= N) return;
+  float acc[HPS_T];
+#pragma unroll
+  for (int t = 0; t < HPS_T; ++t) acc[t] = 0.f;
+  for (int k = lane * 8; k < K; k += 256) {
+    const uint4 raw = k == lane * 8 ? first : *reinterpret_cast<const uint4*>(wrow + k);
+    float wf[8];
+    const uint32_t ww[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      wf[2 * i] = __uint_as_float(ww[i] << 16);
+      wf[2 * i + 1] = __uint_as_float(ww[i] & 0xffff0000u);
+    }
+#pragma unroll
+    for (int t = 0; t < HPS_T; ++t)
+      if (t < T) {
+        const float4 x0 = *reinterpret_cast<const float4*>(xs + t * K + k), x1 = *reinterpret_cast<const float4*>(xs + t * K + k + 4);
+        acc[t] += wf[0] * x0.x + wf[1] * x0.y + wf[2] * x0.z + wf[3] * x0.w + wf[4] * x1.x + wf[5] * x1.y + wf[6] * x1.z + wf[7] * x1.w;
+      }
+  }
+#pragma unroll
+  for (int t = 0; t < HPS_T; ++t)
+    if (t < T) {
+      const float v = warp_sum(acc[t]);
+      if (lane == 0) out[(size_t)t * so_t + (size_t)h * so_h + n] = __float2bfloat16_rn(v);
+    }
+}
 }  // namespace
 
 // proj [S, T, W] float32 partial sums of [q | latent] (W = H (D + R) + (write_kv ? C + R : 0)); q_plain
@@ -691,6 +742,11 @@ extern "C" int flint_head_products(const void* x, long long sx_t, long long sx_h
   if (K <= 0 || (K & 7) || (sx_t & 7) || (sx_h & 7) || ((uintptr_t)x & 15) || ((uintptr_t)w & 15))
     return fail("head_products: K=%d and the strides of x must be multiples of 8, x and w 16-byte aligned", K);
   if (H > 65535 || (N + HP_N - 1) / HP_N > 65535) return fail("head_products: too many heads or outputs");
+  if (T <= HPS_T && (size_t)T * K * sizeof(float) <= 48 * 1024) {
+    launch_pdl(head_products_small_kernel, dim3((N + 7) / 8, H), dim3(256), (size_t)T * K * sizeof(float), stream,
+               (const __nv_bfloat16*)x, sx_t, sx_h, (const __nv_bfloat16*)w, (__nv_bfloat16*)out, so_t, so_h, T, N, K);
+    return check_launch("head_products (few tokens)");
+  }
   dim3 grid((T + HP_M - 1) / HP_M, (N + HP_N - 1) / HP_N, H);
   launch_pdl(head_products_kernel, grid, dim3(128), 0, stream, (const __nv_bfloat16*)x, sx_t, sx_h,
              (const __nv_bfloat16*)w, (__nv_bfloat16*)out, so_t, so_h, T, N, K);

@@ -57,37 +57,52 @@ __device__ __forceinline__ void block_router_logits(const float* __restrict__ x,
   }
   __syncthreads();
   constexpr int VN = Vec<TW>::N;
-  for (int e = warp; e < E; e += ROUTER_WARPS) {
-    const TW* w = wr + (size_t)e * H;
-    float a[TT];
+  constexpr int EW = 4;            // experts a warp works side by side: their weight loads are in flight together
+  for (int e0 = warp * EW; e0 < E; e0 += ROUTER_WARPS * EW) {
+    float a[EW][TT];
 #pragma unroll
-    for (int tt = 0; tt < TT; ++tt) a[tt] = 0.f;
+    for (int k = 0; k < EW; ++k)
+#pragma unroll
+      for (int tt = 0; tt < TT; ++tt) a[k][tt] = 0.f;
     if (vec_ok) {
-#pragma unroll 4
+#pragma unroll 2
       for (int d = lane * VN; d < H; d += 32 * VN) {
-        float wv[VN];
-        load_vec(w + d, wv);
+        float wv[EW][VN];
+#pragma unroll
+        for (int k = 0; k < EW; ++k) {
+          if (e0 + k < E) load_vec(wr + (size_t)(e0 + k) * H + d, wv[k]);
+          else
+#pragma unroll
+            for (int i = 0; i < VN; ++i) wv[k][i] = 0.f;
+        }
 #pragma unroll
         for (int tt = 0; tt < TT; ++tt) {
           float xv[VN];                       // 16-byte reads of the staged row: no bank conflicts
 #pragma unroll
           for (int i = 0; i < VN; i += 4) load_vec(xs + tt * H + d + i, xv + i);
 #pragma unroll
-          for (int i = 0; i < VN; ++i) a[tt] = fmaf(xv[i], wv[i], a[tt]);
+          for (int k = 0; k < EW; ++k)
+#pragma unroll
+            for (int i = 0; i < VN; ++i) a[k][tt] = fmaf(xv[i], wv[k][i], a[k][tt]);
         }
       }
     } else {
       for (int d = lane; d < H; d += 32) {
-        const float wv = to_f32(w[d]);
 #pragma unroll
-        for (int tt = 0; tt < TT; ++tt) a[tt] = fmaf(xs[tt * H + d], wv, a[tt]);
+        for (int k = 0; k < EW; ++k) {
+          const float wv = e0 + k < E ? to_f32(wr[(size_t)(e0 + k) * H + d]) : 0.f;
+#pragma unroll
+          for (int tt = 0; tt < TT; ++tt) a[k][tt] = fmaf(xs[tt * H + d], wv, a[k][tt]);
+        }
       }
     }
 #pragma unroll
-    for (int tt = 0; tt < TT; ++tt) {
-      const float v = warp_sum(a[tt]);
-      if (lane == 0) s_all[tt * E + e] = v;
-    }
+    for (int k = 0; k < EW; ++k)
+#pragma unroll
+      for (int tt = 0; tt < TT; ++tt) {
+        const float v = warp_sum(a[k][tt]);
+        if (lane == 0 && e0 + k < E) s_all[tt * E + e0 + k] = v;
+      }
   }
   __syncthreads();
 }

@@ -282,8 +282,9 @@ def test_pair_table_kernel_keeps_each_request_s_newest_token(ops):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_head_products(ops, dtype):
-    T, H, K, N = 21, 5, 24, 40
+@pytest.mark.parametrize("T", [21, 5, 1, 70])            # many tokens, and the few of a decode step
+def test_head_products(ops, dtype, T):
+    H, K, N = 5, 24, 40
     wide = torch.randn(T, H, K + 8).to(dtype)
     w = torch.randn(H, N, K).to(dtype)
     out_wide = torch.zeros(T, H, N + 16, dtype=dtype, device=DEV)
