@@ -517,8 +517,9 @@ latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ qa, const __nv_bfl
 // ---------------------------------------------------------------------------------------------
 // A small product per head, all heads in one launch: out[t, h, :] = W[h] x[t, h, :] (bfloat16 in and out,
 // float32 sums).  x and out may be views into wider rows (strides in elements).  Block (64 tokens, 64 outputs,
-// head): four warps of 16 tokens each, operands staged in shared memory 32 columns at a time.
-constexpr int HP_M = 64, HP_N = 64, HP_K = 32, HP_S = HP_K + 8;
+// head): four warps of 16 tokens each, operands staged in shared memory 64 columns at a time, the next stage on
+// its way while this one is multiplied.
+constexpr int HP_M = 64, HP_N = 64, HP_K = 64, HP_S = HP_K + 8;
 
 __global__ void __launch_bounds__(128)
 head_products_kernel(const __nv_bfloat16* __restrict__ x, long long sx_t, long long sx_h,
@@ -526,8 +527,8 @@ head_products_kernel(const __nv_bfloat16* __restrict__ x, long long sx_t, long l
                      long long so_h, int T, int N, int K) {
   using flint_attn::ldsm4;
   using flint_attn::mma16816;
-  __shared__ __align__(16) __nv_bfloat16 As[HP_M * HP_S];
-  __shared__ __align__(16) __nv_bfloat16 Bs[HP_N * HP_S];
+  __shared__ __align__(16) __nv_bfloat16 As[2][HP_M * HP_S];      // two stages, filled by asynchronous copies
+  __shared__ __align__(16) __nv_bfloat16 Bs[2][HP_N * HP_S];
   pdl_launch();
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int t0 = blockIdx.x * HP_M, n0 = blockIdx.y * HP_N, h = blockIdx.z;
@@ -536,29 +537,45 @@ head_products_kernel(const __nv_bfloat16* __restrict__ x, long long sx_t, long l
   float acc[HP_N / 8][4];
 #pragma unroll
   for (int i = 0; i < HP_N / 8; ++i) { acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f; }
-  pdl_wait();
-  for (int k0 = 0; k0 < K; k0 += HP_K) {
+  auto fetch = [&](int k0, int st) {            // 16-byte units of both operands; zeros beyond the edges
     for (int c = tid; c < (HP_M + HP_N) * (HP_K / 8); c += 128) {
       const int r = c / (HP_K / 8), cu = c % (HP_K / 8), k = k0 + cu * 8;
-      uint4 v = make_uint4(0u, 0u, 0u, 0u);
+      const __nv_bfloat16* src;
+      uint32_t dst;
+      bool live;
       if (r < HP_M) {
-        if (t0 + r < T && k < K) v = *reinterpret_cast<const uint4*>(xh + (size_t)(t0 + r) * sx_t + k);
-        *reinterpret_cast<uint4*>(As + r * HP_S + cu * 8) = v;
+        live = t0 + r < T && k < K;
+        src = xh + (size_t)(t0 + r) * sx_t + k;
+        dst = smem_addr(As[st] + r * HP_S + cu * 8);
       } else {
         const int n = r - HP_M;
-        if (n0 + n < N && k < K) v = *reinterpret_cast<const uint4*>(wh + (size_t)(n0 + n) * K + k);
-        *reinterpret_cast<uint4*>(Bs + n * HP_S + cu * 8) = v;
+        live = n0 + n < N && k < K;
+        src = wh + (size_t)(n0 + n) * K + k;
+        dst = smem_addr(Bs[st] + n * HP_S + cu * 8);
       }
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(live ? src : x), "r"(live ? 16 : 0) : "memory");
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  pdl_wait();
+  fetch(0, 0);
+  int st = 0;
+  for (int k0 = 0; k0 < K; k0 += HP_K, st ^= 1) {
+    if (k0 + HP_K < K) {
+      fetch(k0 + HP_K, st ^ 1);
+      asm volatile("cp.async.wait_group 1;" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
     }
     __syncthreads();
 #pragma unroll
     for (int kk = 0; kk < HP_K; kk += 16) {
       uint32_t a0, a1, a2, a3;
-      ldsm4(smem_addr(As + (warp * 16 + (lane & 15)) * HP_S + kk + (lane >> 4) * 8), a0, a1, a2, a3);
+      ldsm4(smem_addr(As[st] + (warp * 16 + (lane & 15)) * HP_S + kk + (lane >> 4) * 8), a0, a1, a2, a3);
 #pragma unroll
       for (int nb = 0; nb < HP_N / 8; nb += 2) {
         uint32_t b0, b1, b2, b3;
-        ldsm4(smem_addr(Bs + (nb * 8 + ((lane >> 4) << 3) + (lane & 7)) * HP_S + kk + ((lane >> 3) & 1) * 8), b0, b1, b2, b3);
+        ldsm4(smem_addr(Bs[st] + (nb * 8 + ((lane >> 4) << 3) + (lane & 7)) * HP_S + kk + ((lane >> 3) & 1) * 8), b0, b1, b2, b3);
         mma16816(acc[nb], a0, a1, a2, a3, b0, b1);
         mma16816(acc[nb + 1], a0, a1, a2, a3, b2, b3);
       }
@@ -578,6 +595,7 @@ head_products_kernel(const __nv_bfloat16* __restrict__ x, long long sx_t, long l
     }
   }
 }
+
 // The same for a handful of tokens (decoded tokens): a warp per output (h, n) reads its weight row once, all loads in
 // flight, and forms the dot products with every token's row (staged in shared memory as float32).
 constexpr int HPS_T = 16;        // tokens at most
