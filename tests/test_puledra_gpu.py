@@ -406,3 +406,73 @@ def test_greedy_generation_through_the_entry_point(setup):
         assert eng.generate(prompts, 12) == expected
         assert all(g.pages.pool.used_pages == 0 for g in m.cache.groups) and m.cache.free_slots == 4
     assert eng.scheduler.preemptions > 0
+
+
+# ------------------------------------------------------------------------------------------------ the programs
+
+REPO = __import__("os").path.dirname(__import__("os").path.dirname(__import__("os").path.abspath(__file__)))
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_trace_run_as_a_program(setup, tmp_path, dtype):
+    """bin/trace_run in a process of its own, fed a mixed trace over standard input."""
+    import json
+    import subprocess
+    import sys
+    import numpy as np
+    which, cfg, folder, w, reqs, plain = setup
+    steps = traces.mixed(reqs, seed=5)
+    out_dir = tmp_path / "out"
+    proc = subprocess.run([sys.executable, f"{REPO}/bin/trace_run", "--model", str(folder), "--dtype", dtype, "--out", str(out_dir),
+                           "--max-tokens", str(traces.max_tokens_needed(steps))],
+                          input="".join(json.dumps(s) + "\n" for s in steps), capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert [l for l in proc.stdout.split("\n") if l] == [f"done {s['step']}" for s in steps]
+    exp = traces.expected_rows(steps, plain)
+    errs = []
+    for s in steps:
+        f = out_dir / f"{s['step']}.f32"
+        n = sum(len(e["want"]) for e in s["entries"])
+        assert f.exists() == (n > 0)
+        if n:
+            got = torch.from_numpy(np.fromfile(f, dtype="<f4").reshape(n, cfg["vocab"]))
+            errs.append(rel_err(got, torch.stack(exp[s["step"]])))
+    errs = torch.cat(errs)
+    if dtype == "float32":
+        assert float(errs.max()) < 1e-4
+    else:       # a near-tie of two router scores may fall the other way at a few rows
+        assert int((errs > 4e-2).sum()) <= 0.05 * len(errs) and float(errs.median()) < 2e-2
+
+
+@pytest.mark.parametrize("source", ["folder", "random-config"])
+def test_chat_program_prints_the_plain_arg_max_tokens(tmp_path, source):
+    """bin/flint_chat, token ids in and out, greedy: from a model folder, and with ``--random-config FILE --seed N``,
+    which must give the tokens of the folder that the random-weights mode writes for that configuration and seed."""
+    import json
+    import os
+    import subprocess
+    import sys
+    from flint_b200.engine.loading import write_random_model
+    seed = 4
+    cfg = tiny.P1
+    folder = write_random_model(tmp_path / "model", cfg, seed=seed)
+    prompt = [3, 50, 50, 7, 96, 0, 12, 13, 14, 15, 16]
+    if source == "folder":
+        where = ["--model", str(folder)]
+    else:
+        cfg_file = tmp_path / "only_config.json"
+        cfg_file.write_text(json.dumps(cfg))
+        where = ["--random-config", str(cfg_file)]
+    proc = subprocess.run([sys.executable, f"{REPO}/bin/flint_chat", *where, "--prompt", " ".join(map(str, prompt)), "--max-tokens", "8",
+                           "--temperature", "0", "--seed", str(seed), "--dtype", "float32", "--ctx-size", "128"],
+                          capture_output=True, text=True, timeout=600, env={**os.environ, "VERIFY_IDS": "1"})
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    got = [int(x) for x in proc.stdout.split()]
+    assert "prefill: 11 tok" in proc.stderr and "decode:" in proc.stderr
+    pcfg, w = P.load_model_dir(folder)
+    toks, want = list(prompt), []
+    for _ in range(8):
+        t = int(torch.argmax(P.forward(pcfg, w, toks)[-1]))
+        want.append(t)
+        toks.append(t)
+    assert got == want
