@@ -479,7 +479,7 @@ def run_design_pair(args, pk, rng):
                 m = model.layers[0].parts["mixer"]
                 att_bytes = batch * kv * m.row_w * 2
                 att_flops = sum(2 * m.H * (m.Dk + m.C) * k for k in range(1, ctx + 1))
-                names = ("flint_latent_attention", "flint_head_products", "flint_latent_prepare", "flint_router_topk")
+                names = ("flint_latent_attention", "flint_head_products", "flint_latent_prepare", "flint_router_topk", "flint_row_norm")
             else:
                 nq, nkv, hd = phi["num_attention_heads"], phi["num_key_value_heads"], phi["head_dim"]
                 att_bytes = batch * kv * nkv * hd * 2 * 2

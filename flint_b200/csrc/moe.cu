@@ -7,6 +7,7 @@
 #include <math.h>
 #include <stdarg.h>
 #include "common.cuh"
+#include "router_select.cuh"
 
 using namespace flint;
 
@@ -152,7 +153,7 @@ router_sparsemixer_kernel(const float* __restrict__ x, const TW* __restrict__ wr
 // neighbours, a group scores as its best member, only members of the `keep` best groups may be chosen, and the
 // `top` best of those are (lowest index first among equals).  Gates: s_e / (sum of the chosen s + 1e-20) * scale.
 // One warp per token does the selection (a lane holds every 32nd expert); everything is float32.
-constexpr int MAX_TOP = 16;
+constexpr int MAX_TOP = ROUTER_MAX_TOP;
 template <typename TW>
 __global__ void __launch_bounds__(ROUTER_WARPS * 32)
 router_topk_kernel(const float* __restrict__ x, const TW* __restrict__ wr, int top, int n_groups, int keep,
@@ -166,93 +167,14 @@ router_topk_kernel(const float* __restrict__ x, const TW* __restrict__ wr, int t
   const int t0 = blockIdx.x * TT;
   const int nt = min(TT, T - t0);
   block_router_logits<TW>(x, wr, xs, s_all, t0, nt, H, E, vec_ok);
-  // one warp per token: lane l holds experts l, l + 32, ...
+  // one warp per token
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (warp >= nt) return;
   const int t = t0 + warp;
   float* s = s_all + warp * E;
-  constexpr int EPL = MAX_E / 32;
-  float v[EPL];
-  float m = -INFINITY;
-#pragma unroll
-  for (int i = 0; i < EPL; ++i) {
-    const int e = lane + 32 * i;
-    v[i] = e < E ? s[e] : -INFINITY;
-    if (logits_out && e < E) logits_out[(size_t)t * E + e] = v[i];
-    m = fmaxf(m, v[i]);
-  }
-  m = warp_max(m);
-  float denom = 0.f;
-#pragma unroll
-  for (int i = 0; i < EPL; ++i) {
-    v[i] = lane + 32 * i < E ? expf(v[i] - m) : 0.f;
-    denom += v[i];
-  }
-  denom = warp_sum(denom);
-  __syncwarp();
-#pragma unroll
-  for (int i = 0; i < EPL; ++i) {
-    const int e = lane + 32 * i;
-    v[i] = e < E ? v[i] / denom : -1.f;          // scores; -1 marks what cannot be chosen
-    if (e < E) s[e] = v[i];
-  }
-  __syncwarp();
-  // the best of (value, index) pairs over the warp: the larger value, the lower index among equals
-  auto best_of_warp = [&](float& val, int& idx) {
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      const float ov = __shfl_xor_sync(0xffffffffu, val, o);
-      const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
-      if (ov > val || (ov == val && oi < idx)) { val = ov; idx = oi; }
-    }
-  };
-  const int per = E / n_groups;
-  unsigned long long kept = ~0ull;
-  if (keep < n_groups) {
-    float gs[2];                                  // the scores of groups lane and lane + 32
-#pragma unroll
-    for (int k = 0; k < 2; ++k) {
-      const int g = lane + 32 * k;
-      gs[k] = -1.f;
-      if (g < n_groups)
-        for (int e = g * per; e < (g + 1) * per; ++e) gs[k] = fmaxf(gs[k], s[e]);
-    }
-    kept = 0ull;
-    for (int r = 0; r < keep; ++r) {
-      float val = gs[0];
-      int idx = lane;
-      if (gs[1] > val) { val = gs[1]; idx = lane + 32; }
-      best_of_warp(val, idx);
-      kept |= 1ull << idx;
-      if ((idx & 31) == lane) gs[idx >> 5] = -2.f;
-    }
-#pragma unroll
-    for (int i = 0; i < EPL; ++i) {
-      const int e = lane + 32 * i;
-      if (e < E && !(kept >> (e / per) & 1ull)) v[i] = -1.f;
-    }
-  }
-  float my_val = 0.f, sum = 0.f;
-  int my_sel = 0;
-  for (int r = 0; r < top; ++r) {
-    float val = -1.f;
-    int idx = 0x7fffffff;
-#pragma unroll
-    for (int i = 0; i < EPL; ++i)
-      if (v[i] > val) { val = v[i]; idx = lane + 32 * i; }
-    best_of_warp(val, idx);
-    if ((idx & 31) == lane) {
-#pragma unroll
-      for (int i = 0; i < EPL; ++i)
-        if (i == (idx >> 5)) v[i] = -1.f;
-    }
-    if (lane == r) { my_val = val; my_sel = idx; }
-    sum += val;
-  }
-  if (lane < top) {
-    expert_ids[(size_t)t * top + lane] = my_sel;
-    gates[(size_t)t * top + lane] = my_val / (sum + 1e-20f) * out_scale;
-  }
+  if (logits_out)
+    for (int e = lane; e < E; e += 32) logits_out[(size_t)t * E + e] = s[e];
+  select_topk_by_warp(s, lane, E, top, n_groups, keep, out_scale, expert_ids + (size_t)t * top, gates + (size_t)t * top);
 }
 
 // One block.  expert_ids [T*top] -> per-expert counts, offsets (exclusive scan), the sorted row

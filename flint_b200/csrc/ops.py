@@ -215,7 +215,8 @@ class CudaOps:
         fused kernel does not take."""
         _check(x, "x", torch.float32, 2)
         T, H = x.shape
-        if H % 4 or H > 16384 or (router is not None and (row_index is not None or H * 4 > 160000)):
+        if H % 4 or H > 16384 or (router is not None and (row_index is not None or H * 4 > 160000
+                                                          or router.weight.shape[0] > H)):
             if pending is not None:
                 self.apply_pending(x, pending)
             tmp = out_f32
@@ -223,8 +224,7 @@ class CudaOps:
                 tmp = torch.empty((T, H), dtype=torch.float32, device=x.device)
             self.norm(x, gamma, beta, eps, mode, out_f32=tmp, out_bf16=out_bf16, row_index=row_index)
             if router is not None:
-                self.router_sparsemixer(tmp, router.weight, router.jitter_eps, router.expert_ids, router.gates,
-                                        getattr(router, "logits", None))
+                self.route(tmp, router)
             return
         rows = row_index.numel() if row_index is not None else T
         for o, dt in ((out_f32, torch.float32), (out_bf16, torch.bfloat16)):
@@ -251,21 +251,24 @@ class CudaOps:
                     raise KernelError("row_norm: pending expert rows do not match the residual")
         wr = logits = None
         E, jit, ids, gates = 0, 0.0, None, None
+        r_top, r_groups, r_keep, r_scale = 0, 1, 1, 1.0
         if router is not None:
             wr, E, jit, ids, gates = router.weight, router.weight.shape[0], router.jitter_eps, router.expert_ids, router.gates
             logits = getattr(router, "logits", None)
+            r_top, r_groups = int(getattr(router, "top", 0)), int(getattr(router, "groups", 1))
+            r_keep, r_scale = int(getattr(router, "keep", 1)), float(getattr(router, "scale", 1.0))
             if logits is not None:
                 _check(logits, "router logits", torch.float32, 2)
                 if tuple(logits.shape) != (T, E):
                     raise KernelError(f"row_norm: router logits must be [{T}, {E}]")
             _check(wr, "router weight", dims=2)
-            if wr.shape[1] != H or ids.numel() != 2 * T or gates.numel() != 2 * T:
+            if wr.shape[1] != H or ids.numel() != (r_top or 2) * T or gates.numel() != (r_top or 2) * T:
                 raise KernelError("row_norm: router shapes do not match")
         self._run("row_fused", "flint_row_norm", _ptr(x), _ptr(row_index), c_int(rows), c_int(H), _ptr(partials),
                   c_int(S), c_longlong(stride), _ptr(bias), _ptr(y), _ptr(row_of), _ptr(gts), c_int(top), _ptr(gamma), _ptr(beta),
                   c_float(eps), c_int({"layer": 0, "rms": 1}[mode]), _ptr(out_f32), _ptr(out_bf16), _ptr(wr),
                   c_int(_code(wr.dtype) if wr is not None else 0), c_int(E), c_float(jit), _ptr(ids), _ptr(gates),
-                  _ptr(logits))
+                  _ptr(logits), c_int(r_top), c_int(r_groups), c_int(r_keep), c_float(r_scale))
 
     def apply_pending(self, x, pending):
         """x += what a part left pending (for a norm that cannot take it along)."""
@@ -846,6 +849,14 @@ class CudaOps:
         _check(gates, "gates", torch.float32)
         self._run("moe", "flint_router_sparsemixer", _ptr(x), _ptr(wr), c_int(_code(wr.dtype)), c_float(eps),
                   _ptr(expert_ids), _ptr(gates), _ptr(logits_out), c_int(T), c_int(H), c_int(E))
+
+    def route(self, x, router):
+        """Serve a ``RouterRequest`` on normalised rows x [T, H] float32 with the stand-alone kernels."""
+        if int(getattr(router, "top", 0)) > 0:
+            return self.router_topk(x, router.weight, router.top, router.groups, router.keep, router.scale,
+                                    router.expert_ids, router.gates, getattr(router, "logits", None))
+        return self.router_sparsemixer(x, router.weight, router.jitter_eps, router.expert_ids, router.gates,
+                                       getattr(router, "logits", None))
 
     def router_topk(self, x, wr, top, n_groups, keep, scale, expert_ids, gates, logits_out=None):
         """Softmax router whose choice is limited to groups: scores softmax(x @ wr.T) in float32; the experts form

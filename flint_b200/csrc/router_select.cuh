@@ -1,0 +1,102 @@
+// The choice of a softmax router limited to groups, by one warp, from float32 logits in shared memory.
+//
+//   s = softmax(logits); the E experts form n_groups equal groups of neighbours; a group scores as its best member;
+//   only members of the `keep` best groups may be chosen; the `top` best of those are (the lower index among
+//   equals); gates: s_e / (sum of the chosen s + 1e-20) * out_scale.
+//
+// Shared by the stand-alone router kernel (moe.cu) and the row kernel that routes while it has the normalised row
+// (row_fused.cu).  `s` holds the logits on entry and the scores afterwards; all 32 lanes of the warp call.
+#pragma once
+#include <math.h>
+#include "common.cuh"
+
+namespace flint {
+
+constexpr int ROUTER_MAX_E = 256;       // experts at most
+constexpr int ROUTER_MAX_TOP = 16;      // choices a token at most
+
+__device__ __forceinline__ void select_topk_by_warp(float* s, int lane, int E, int top, int n_groups, int keep,
+                                                    float out_scale, int* ids, float* gates) {
+  constexpr int EPL = ROUTER_MAX_E / 32;   // lane l holds experts l, l + 32, ...
+  float v[EPL];
+  float m = -INFINITY;
+#pragma unroll
+  for (int i = 0; i < EPL; ++i) {
+    const int e = lane + 32 * i;
+    v[i] = e < E ? s[e] : -INFINITY;
+    m = fmaxf(m, v[i]);
+  }
+  m = warp_max(m);
+  float denom = 0.f;
+#pragma unroll
+  for (int i = 0; i < EPL; ++i) {
+    v[i] = lane + 32 * i < E ? expf(v[i] - m) : 0.f;
+    denom += v[i];
+  }
+  denom = warp_sum(denom);
+  __syncwarp();
+#pragma unroll
+  for (int i = 0; i < EPL; ++i) {
+    const int e = lane + 32 * i;
+    v[i] = e < E ? v[i] / denom : -1.f;          // scores; -1 marks what cannot be chosen
+    if (e < E) s[e] = v[i];
+  }
+  __syncwarp();
+  // the best of (value, index) pairs over the warp: the larger value, the lower index among equals
+  auto best_of_warp = [&](float& val, int& idx) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, val, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+      if (ov > val || (ov == val && oi < idx)) { val = ov; idx = oi; }
+    }
+  };
+  const int per = E / n_groups;
+  if (keep < n_groups) {
+    float gs[2];                                  // the scores of groups lane and lane + 32
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+      const int g = lane + 32 * k;
+      gs[k] = -1.f;
+      if (g < n_groups)
+        for (int e = g * per; e < (g + 1) * per; ++e) gs[k] = fmaxf(gs[k], s[e]);
+    }
+    unsigned long long kept = 0ull;
+    for (int r = 0; r < keep; ++r) {
+      float val = gs[0];
+      int idx = lane;
+      if (gs[1] > val) { val = gs[1]; idx = lane + 32; }
+      best_of_warp(val, idx);
+      kept |= 1ull << idx;
+      if ((idx & 31) == lane) gs[idx >> 5] = -2.f;
+    }
+#pragma unroll
+    for (int i = 0; i < EPL; ++i) {
+      const int e = lane + 32 * i;
+      if (e < E && !((kept >> (e / per)) & 1ull)) v[i] = -1.f;
+    }
+  }
+  float my_val = 0.f, sum = 0.f;
+  int my_sel = 0;
+  for (int r = 0; r < top; ++r) {
+    float val = -1.f;
+    int idx = 0x7fffffff;
+#pragma unroll
+    for (int i = 0; i < EPL; ++i)
+      if (v[i] > val) { val = v[i]; idx = lane + 32 * i; }
+    best_of_warp(val, idx);
+    if ((idx & 31) == lane) {
+#pragma unroll
+      for (int i = 0; i < EPL; ++i)
+        if (i == (idx >> 5)) v[i] = -1.f;
+    }
+    if (lane == r) { my_val = val; my_sel = idx; }
+    sum += val;
+  }
+  if (lane < top) {
+    ids[lane] = my_sel;
+    gates[lane] = my_val / (sum + 1e-20f) * out_scale;
+  }
+}
+
+}  // namespace flint

@@ -54,15 +54,21 @@ class Pending:
 
 @dataclass
 class RouterRequest:
-    """What a feed-forward asks a norm to compute while the normalised row is at hand: router
-    logits over ``weight`` [E, H], sparsemixer top-2 with ``jitter_eps``, into ``expert_ids`` and
-    ``gates`` ([T, 2] each).  ``logits`` ([T, E] float32, optional): the logits the choice was made from
-    are written there too (tests compare them)."""
+    """What a feed-forward asks a norm to compute while the normalised row is at hand: router logits over
+    ``weight`` [E, H] and the choice of experts, into ``expert_ids`` and ``gates`` ([T, k] each).  The rule is
+    sparsemixer top-2 with ``jitter_eps`` (``top`` 0), or, with ``top`` > 0, a softmax whose choice is limited to
+    the ``keep`` best of ``groups`` equal groups of neighbouring experts, ``top`` experts a token, gates times
+    ``scale``.  ``logits`` ([T, E] float32, optional): the logits the choice was made from are written there too
+    (tests compare them)."""
     weight: torch.Tensor
     jitter_eps: float
     expert_ids: torch.Tensor
     gates: torch.Tensor
     logits: torch.Tensor | None = None
+    top: int = 0
+    groups: int = 1
+    keep: int = 1
+    scale: float = 1.0
 
 
 @dataclass

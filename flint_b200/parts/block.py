@@ -87,9 +87,16 @@ class ParallelBlock(Block):
     def forward(self, residual, step, cache, state, writes_cache=True, carry=None):
         p = self.parts
         ffn = p.get("ffn")
-        want = tuple(set(p["mixer"].input_dtypes()) | set(ffn.input_dtypes() if ffn is not None else ()))
-        x, _ = run_norm(p["norm1"], residual, want, carry)
+        # a feed-forward that routes may have its routing done by the one norm, while the row is at hand
+        request = ffn.router_request(residual.shape[0]) if hasattr(ffn, "router_request") else None
+        routed_by_norm = request is not None and p["norm1"].supports_router
+        if routed_by_norm and step.record is not None and getattr(request, "logits", 0) is None:
+            request.logits = request.weight.new_empty((residual.shape[0], request.weight.shape[0]), dtype=torch.float32)
+        ffn_want = () if ffn is None else (ffn.input_dtypes_when_routed() if routed_by_norm else ffn.input_dtypes())
+        want = tuple(set(p["mixer"].input_dtypes()) | set(ffn_want))
+        x, routed = run_norm(p["norm1"], residual, want, carry, request if routed_by_norm else None)
         mixed = p["mixer"].forward(x, residual, step, cache, state, writes_cache)
         if ffn is None:
             return mixed
-        return merge_pending(p["mixer"], residual, mixed, ffn.forward(x, residual, step))
+        fed = ffn.forward(x, residual, step, routed=routed) if routed is not None else ffn.forward(x, residual, step)
+        return merge_pending(p["mixer"], residual, mixed, fed)

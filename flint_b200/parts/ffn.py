@@ -169,14 +169,27 @@ class GroupedTopKMoE(FeedForward):
     def input_dtypes(self):
         return (torch.float32, self.w13.dtype)       # the router reads the float32 rows
 
-    def forward(self, x, residual, step):
+    def router_request(self, n_rows):
+        """Routing can ride on the norm before this part (the normalised row is in registers there)."""
+        dev = self.w_router.device
+        return RouterRequest(self.w_router, 0.0, torch.empty((n_rows, self.top), dtype=torch.int32, device=dev),
+                             torch.empty((n_rows, self.top), dtype=torch.float32, device=dev), top=self.top,
+                             groups=self.groups, keep=self.keep, scale=self.router_scale)
+
+    def input_dtypes_when_routed(self):
+        return (self.w13.dtype,)
+
+    def forward(self, x, residual, step, routed=None):
         ops = self.ops
         xa = x[self.w13.dtype]
         T, dev, k = xa.shape[0], xa.device, self.top
-        ids = torch.empty((T, k), dtype=torch.int32, device=dev)
-        gates = torch.empty((T, k), dtype=torch.float32, device=dev)
-        logits = torch.empty((T, self.E), dtype=torch.float32, device=dev) if step.record is not None else None
-        ops.router_topk(x[torch.float32], self.w_router, k, self.groups, self.keep, self.router_scale, ids, gates, logits)
+        if routed is not None:
+            ids, gates, logits = routed.expert_ids, routed.gates, routed.logits
+        else:
+            ids = torch.empty((T, k), dtype=torch.int32, device=dev)
+            gates = torch.empty((T, k), dtype=torch.float32, device=dev)
+            logits = torch.empty((T, self.E), dtype=torch.float32, device=dev) if step.record is not None else None
+            ops.router_topk(x[torch.float32], self.w_router, k, self.groups, self.keep, self.router_scale, ids, gates, logits)
         plan, xs = ops.moe_dispatch(ids, self.E, ops.moe_tile_rows(T, self.E, self.w13.dtype, k), xa)
         a = torch.empty((k * T, self.inter), dtype=self.w13.dtype, device=dev)
         ops.gated_gemm(xs, self.w13, a, self.act, plan)
@@ -185,6 +198,7 @@ class GroupedTopKMoE(FeedForward):
         if step.record is not None:
             step.record.setdefault("experts", []).append(ids)
             step.record.setdefault("gates", []).append(gates)
-            step.record.setdefault("router_logits", []).append(logits)
+            if logits is not None:
+                step.record.setdefault("router_logits", []).append(logits)
         # the weighted sum of the chosen experts' rows is added by the next norm's kernel
         return Pending(y=y, row_of=plan.row_of, gates=gates)

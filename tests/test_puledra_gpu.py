@@ -233,6 +233,36 @@ def test_router_topk(ops, wdtype, E, top, groups, keep):
         assert (gates[t].double().cpu() - torch.tensor(e_w)).abs().max() < 1e-5
 
 
+@pytest.mark.parametrize("wdtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("T,H", [(41, 72), (5, 2048), (300, 2048)])     # a block a row; a cluster of blocks a row; many rows
+@pytest.mark.parametrize("E,top,groups,keep", [(12, 3, 3, 2), (64, 6, 8, 3), (6, 1, 1, 1)])
+def test_router_rides_on_the_norm(ops, wdtype, T, H, E, top, groups, keep):
+    """The norm's kernel fills a routing request for the grouped softmax rule: the same experts and gates as the
+    plain rule on the plain norm of the rows."""
+    from flint_b200.parts.base import RouterRequest
+    x = torch.randn(T, H)
+    gamma = 1.0 + 0.1 * torch.randn(H)
+    wr = (torch.randn(E, H) * (3.0 / math.sqrt(H))).to(wdtype)
+    req = RouterRequest(wr.to(DEV), 0.0, torch.zeros(T, top, dtype=torch.int32, device=DEV),
+                        torch.zeros(T, top, dtype=torch.float32, device=DEV),
+                        logits=torch.zeros(T, E, dtype=torch.float32, device=DEV), top=top, groups=groups, keep=keep, scale=2.5)
+    out = torch.zeros(T, H, dtype=torch.bfloat16, device=DEV)
+    ops.row_norm(x.clone().to(DEV), gamma.to(DEV), None, 1e-5, "rms", out_bf16=out, router=req)
+    n = P.rms_norm(x.double(), gamma.double(), 1e-5)
+    z = n @ wr.double().T
+    assert (req.logits.double().cpu() - z).abs().max() < 2e-4
+    same = 0
+    for t in range(T):
+        e_ids, e_w = P.route(z[t], top, groups, keep, 2.5)
+        if req.expert_ids[t].tolist() == e_ids:
+            same += 1
+            assert (req.gates[t].double().cpu() - torch.tensor(e_w)).abs().max() < 1e-4
+        else:       # only where two scores are within rounding of each other
+            e2, _ = P.route(req.logits[t].double().cpu(), top, groups, keep, 2.5)
+            assert req.expert_ids[t].tolist() == e2
+    assert same >= T - 2
+
+
 @pytest.mark.parametrize("H", [64, 50, 4096])
 def test_pending_rows_of_three_experts_join_the_norm(ops, H):
     T, k, S = 19, 3, 2
