@@ -28,11 +28,12 @@ from .pages import NO_PAGE, GroupPages
 class KVSpec:
     """What a mixer needs cached per token: ``num_kv_heads`` keys of ``head_dim`` numbers and as many values of
     ``value_dim`` numbers (default: as wide as the keys; 0: keys only).  ``window`` 0 means every key stays
-    reachable; otherwise only the last ``window`` positions."""
+    reachable; otherwise only the last ``window`` positions, and the first ``keep_first`` of the sequence."""
     num_kv_heads: int
     head_dim: int
     window: int = 0
     value_dim: int | None = None
+    keep_first: int = 0
 
     @property
     def value_width(self) -> int:
@@ -58,7 +59,7 @@ class GroupCache:
         if torch.device(device).type == "cuda":
             self._host_table = self._host_table.pin_memory()
         pages = GroupPages(n_pages, page_size, spec.window, max_slots, max_pages_per_request,
-                           host_table_ptr=self._host_table.data_ptr())
+                           host_table_ptr=self._host_table.data_ptr(), keep_first=spec.keep_first)
         self.pages = pages
         P = pages.page_size
         n = pages.pool.n_pages

@@ -106,13 +106,16 @@ class GroupPages:
     the tables (the block table that is copied to the device)."""
 
     def __init__(self, n_pages: int, page_size: int, window: int, max_slots: int, max_pages_per_request: int,
-                 host_table_ptr=None):
+                 host_table_ptr=None, keep_first: int = 0):
         self.page_size = int(page_size)
         self.window = int(window)          # 0 = every key is kept
+        self.keep_first = int(keep_first) if self.window else 0   # positions that stay reachable behind the window
         self.max_pages_per_request = int(max_pages_per_request)
         self._n = _Native(int(n_pages), self.page_size, self.window, int(max_slots), self.max_pages_per_request,
                           host_table_ptr)
         self._lib = self._n.lib
+        if self.keep_first:
+            rt.checked(self._lib.flint_rt_group_set_keep_first(self._n.handle, self.keep_first))
         self.pool = PagePool(n_pages, self._n)
         self.tables = [PageTable(self._n, s, self.max_pages_per_request) for s in range(max_slots)]
 

@@ -1,0 +1,335 @@
+// Paged attention in its general form: keys and values of different sizes, a sliding window that keeps a
+// request's first tokens, and a learned sink logit per query head in the softmax's denominator.
+//
+// A query row t at position p of request slot[t] sees key j of its request if j <= p and (p - j < window or
+// j < keep_first); window 0: every j <= p.  The seen keys are numbered without gaps: first the kept ones below
+// the window's start (positions 0 .. min(keep_first, lo) - 1, lo = max(0, p + 1 - window)), then lo .. p; a split
+// of the key range is a run of these numbers.  Kept tokens keep their positions: they were rotated where they
+// stand, and nothing is rotated again.  With a sink s_h the weights are e^(score_j - M) / (sum_j e^(score_j - M)
+// + e^(s_h - M)): the sink takes part in the maximum and the sum and has no value.  Scores, maxima, sums and the
+// output are float32 (online softmax over blocks of 32 keys).
+//
+// flint_qkv_write makes q and the cache rows from the projection: it adds up the partial sums and the bias,
+// rotates the leading `rot` dims of every query and key head by the token's position, optionally leaves the
+// values as projected for later layers (v_keep) or blends them with an earlier layer's (v = (1 - a) v + a v_from),
+// and writes keys [page, kv head, P, hd] and values [page, kv head, P, vd] into the token's page.
+//
+// Work of flint_sink_attention is split as (row, kv head, chunk of up to 4 query heads, split): one warp each;
+// a lane owns a key in the score phase and value dims lane, lane + 32, ... in the value phase.  With several
+// splits a second kernel merges (max, sum, unnormalised output) records in a fixed order and adds the sink.
+// Head sizes up to 256; rows of whole 16-byte units are read in such units, others element by element.
+//
+// The reference's attention has the causal and window mask only (crates/thuban_kernel/wgsl/attn.wgsl:78-90).
+#include <math.h>
+#include <stdarg.h>
+#include "common.cuh"
+
+using namespace flint;
+
+namespace {
+
+constexpr int GC = 4;          // query heads per warp
+constexpr int WARPS = 4;
+constexpr int MAX_DPL = 8;     // value dims per lane: vd <= 256
+
+template <typename TC> struct Vec8;
+template <> struct Vec8<float> {
+  static __device__ __forceinline__ void load(const float* p, float* f) {
+    const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+    f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+  }
+};
+template <> struct Vec8<__nv_bfloat16> {
+  static __device__ __forceinline__ void load(const __nv_bfloat16* p, float* f) {
+    const uint4 a = *reinterpret_cast<const uint4*>(p);
+    const uint32_t w[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      f[2 * i] = __uint_as_float(w[i] << 16);
+      f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    }
+  }
+};
+
+// ------------------------------------------------------------------------------------------- q and the cache rows
+template <typename TQ, typename TC>
+__global__ void qkv_write_kernel(const float* __restrict__ qkv, int n_partials, long long partial_stride,
+                                 const float* __restrict__ bias, const int* __restrict__ pos, const int* __restrict__ slot,
+                                 const float* __restrict__ cos_t, const float* __restrict__ sin_t, int rot, int interleaved,
+                                 TQ* __restrict__ q_out, TC* __restrict__ k_cache, TC* __restrict__ v_cache,
+                                 const int* __restrict__ block_table, int max_pages, int page_size, int nq, int nkv,
+                                 int hd, int vd, float* __restrict__ v_keep, const float* __restrict__ v_from, float blend,
+                                 int* __restrict__ status) {
+  pdl_launch();
+  pdl_wait();
+  const int t = blockIdx.x;
+  const int p = pos[t];
+  const int lp = p / page_size;
+  const int page = lp < max_pages ? block_table[(size_t)slot[t] * max_pages + lp] : -1;
+  if (page < 0 && threadIdx.x == 0) atomicExch(status, 1);
+  const int qk_w = (nq + nkv) * hd, W = qk_w + nkv * vd, half = rot / 2;
+  const float* row = qkv + (size_t)t * W;
+  auto value = [&](int e) {
+    float x = 0.f;
+    for (int z = 0; z < n_partials; ++z) x += row[(size_t)z * partial_stride + e];
+    return bias ? x + bias[e] : x;
+  };
+  for (int e = threadIdx.x; e < W; e += blockDim.x) {
+    float x = value(e);
+    if (e < qk_w) {
+      const int head = e / hd, d = e % hd;
+      if (d < rot) {
+        int i, partner;
+        bool first;
+        if (interleaved) { i = d >> 1; first = !(d & 1); partner = first ? e + 1 : e - 1; }
+        else { i = d < half ? d : d - half; first = d < half; partner = first ? e + half : e - half; }
+        const float y = value(partner);
+        const float c = cos_t[(size_t)p * half + i], s = sin_t[(size_t)p * half + i];
+        x = first ? x * c - y * s : x * c + y * s;
+      }
+      if (head < nq) {
+        q_out[(size_t)t * nq * hd + e] = from_f32<TQ>(x);
+      } else if (page >= 0) {
+        k_cache[(((size_t)page * nkv + (head - nq)) * page_size + p % page_size) * hd + d] = from_f32<TC>(x);
+      }
+    } else {
+      const int ev = e - qk_w, kvh = ev / vd, d = ev % vd;
+      if (v_keep) v_keep[(size_t)t * nkv * vd + ev] = x;
+      if (v_from) x = (1.0f - blend) * x + blend * v_from[(size_t)t * nkv * vd + ev];
+      if (page >= 0) v_cache[(((size_t)page * nkv + kvh) * page_size + p % page_size) * vd + d] = from_f32<TC>(x);
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------- attention
+template <typename TQ, typename TC, typename TO>
+__global__ void __launch_bounds__(WARPS * 32)
+sink_attention_kernel(const TQ* __restrict__ q, const TC* __restrict__ k_cache, const TC* __restrict__ v_cache,
+                      const int* __restrict__ block_table, int max_pages, int page_size, const int* __restrict__ pos,
+                      const int* __restrict__ slot, TO* __restrict__ out, float* __restrict__ scratch, int T, int nq,
+                      int nkv, int hd, int vd, int window, int keep_first, const float* __restrict__ sinks, float scale,
+                      int split_keys, int n_splits, int g_chunks) {
+  extern __shared__ float smem[];  // per warp: GC * hd floats of q
+  pdl_launch();
+  pdl_wait();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long long item = (long long)blockIdx.x * WARPS + warp;
+  if (item >= (long long)T * nkv * g_chunks * n_splits) return;
+  const int split = (int)(item % n_splits);
+  long long rest = item / n_splits;
+  const int gchunk = (int)(rest % g_chunks);
+  rest /= g_chunks;
+  const int kvh = (int)(rest % nkv);
+  const int t = (int)(rest / nkv);
+  const int G = nq / nkv, g0 = gchunk * GC, ng = min(GC, G - g0), h0 = kvh * G + g0;
+  const int p = pos[t];
+  const int lo = window > 0 ? max(0, p + 1 - window) : 0;
+  const int n_first = min(keep_first, lo);              // kept keys below the window's start
+  const int total = n_first + (p + 1 - lo);             // seen keys, numbered 0 .. total - 1
+  const int u_lo = split * split_keys, u_hi = min(total, u_lo + split_keys);
+  const int* bt = block_table + (size_t)slot[t] * max_pages;
+
+  float* qs = smem + warp * GC * hd;
+  for (int i = lane; i < ng * hd; i += 32) qs[i] = to_f32(q[((size_t)t * nq + h0) * hd + i]) * scale;
+  __syncwarp();
+
+  const bool k_vec = (hd % 8) == 0;
+  const int dpl = (vd + 31) / 32;
+  float m[GC], l[GC], acc[GC][MAX_DPL];
+#pragma unroll
+  for (int g = 0; g < GC; ++g) {
+    m[g] = -INFINITY;
+    l[g] = 0.f;
+#pragma unroll
+    for (int i = 0; i < MAX_DPL; ++i) acc[g][i] = 0.f;
+  }
+
+  for (int u0 = u_lo; u0 < u_hi; u0 += 32) {
+    const int u = u0 + lane;
+    long long row = -1;   // index of the key's row in [page, kv_head, P] units
+    if (u < u_hi) {
+      const int j = u < n_first ? u : lo + (u - n_first);
+      const int page = bt[j / page_size];
+      if (page >= 0) row = ((long long)page * nkv + kvh) * page_size + (j % page_size);
+    }
+    float s[GC];
+#pragma unroll
+    for (int g = 0; g < GC; ++g) s[g] = 0.f;
+    if (row >= 0) {
+      const TC* kr = k_cache + row * hd;
+      if (k_vec) {
+        for (int d = 0; d < hd; d += 8) {
+          float kf[8];
+          Vec8<TC>::load(kr + d, kf);
+#pragma unroll
+          for (int g = 0; g < GC; ++g)
+            if (g < ng) {
+#pragma unroll
+              for (int e = 0; e < 8; ++e) s[g] = fmaf(qs[g * hd + d + e], kf[e], s[g]);
+            }
+        }
+      } else {
+        for (int d = 0; d < hd; ++d) {
+          const float kf = to_f32(kr[d]);
+#pragma unroll
+          for (int g = 0; g < GC; ++g)
+            if (g < ng) s[g] = fmaf(qs[g * hd + d], kf, s[g]);
+        }
+      }
+    }
+    float pr[GC];
+#pragma unroll
+    for (int g = 0; g < GC; ++g) {
+      const float sg = row >= 0 ? s[g] : -INFINITY;
+      const float m_new = fmaxf(m[g], warp_max(sg));
+      const bool any = m_new > -INFINITY;
+      const float alpha = any ? expf(m[g] - m_new) : 1.f;
+      pr[g] = (any && row >= 0) ? expf(sg - m_new) : 0.f;
+      l[g] = l[g] * alpha + warp_sum(pr[g]);
+      m[g] = m_new;
+#pragma unroll
+      for (int i = 0; i < MAX_DPL; ++i) acc[g][i] *= alpha;
+    }
+    const int nk = min(32, u_hi - u0);
+    for (int jj = 0; jj < nk; ++jj) {
+      const long long vrow = __shfl_sync(0xffffffffu, row, jj);
+      float pj[GC];
+#pragma unroll
+      for (int g = 0; g < GC; ++g) pj[g] = __shfl_sync(0xffffffffu, pr[g], jj);
+      if (vrow < 0) continue;
+      const TC* vr = v_cache + vrow * vd;
+#pragma unroll
+      for (int i = 0; i < MAX_DPL; ++i) {
+        const int d = lane + 32 * i;
+        if (i < dpl && d < vd) {
+          const float vv = to_f32(vr[d]);
+#pragma unroll
+          for (int g = 0; g < GC; ++g) acc[g][i] = fmaf(pj[g], vv, acc[g][i]);
+        }
+      }
+    }
+  }
+
+  if (n_splits == 1) {
+#pragma unroll
+    for (int g = 0; g < GC; ++g)
+      if (g < ng) {
+        float scale_o = 1.f, sum = l[g];
+        if (sinks) {      // the sink joins the maximum and the sum
+          const float sk = sinks[h0 + g], m_all = fmaxf(m[g], sk);
+          scale_o = m[g] > -INFINITY ? expf(m[g] - m_all) : 0.f;
+          sum = l[g] * scale_o + expf(sk - m_all);
+        }
+        const float inv = sum > 0.f ? scale_o / sum : 0.f;
+#pragma unroll
+        for (int i = 0; i < MAX_DPL; ++i) {
+          const int d = lane + 32 * i;
+          if (i < dpl && d < vd) out[((size_t)t * nq + h0 + g) * vd + d] = from_f32<TO>(acc[g][i] * inv);
+        }
+      }
+  } else {
+    // scratch [T, nq, n_splits, vd + 2]: unnormalised output, then max, then sum
+#pragma unroll
+    for (int g = 0; g < GC; ++g)
+      if (g < ng) {
+        float* dst = scratch + (((size_t)t * nq + h0 + g) * n_splits + split) * (vd + 2);
+#pragma unroll
+        for (int i = 0; i < MAX_DPL; ++i) {
+          const int d = lane + 32 * i;
+          if (i < dpl && d < vd) dst[d] = acc[g][i];
+        }
+        if (lane == 0) {
+          dst[vd] = m[g];
+          dst[vd + 1] = l[g];
+        }
+      }
+  }
+}
+
+// Merge the splits of one (row, head) and add the sink: out = sum_s e^(m_s - M) o_s / (sum_s e^(m_s - M) l_s + e^(sink - M)).
+template <typename TO>
+__global__ void sink_combine_kernel(const float* __restrict__ scratch, TO* __restrict__ out, int vd, int n_splits, int nq,
+                                    const float* __restrict__ sinks) {
+  pdl_launch();
+  pdl_wait();
+  const size_t rh = blockIdx.x;   // row * nq + head
+  const float* base = scratch + rh * n_splits * (vd + 2);
+  const float sk = sinks ? sinks[rh % nq] : -INFINITY;
+  float M = sk;
+  for (int s = 0; s < n_splits; ++s) M = fmaxf(M, base[(size_t)s * (vd + 2) + vd]);
+  float L = sinks ? expf(sk - M) : 0.f;
+  for (int s = 0; s < n_splits; ++s) {           // fixed order, the same in every thread
+    const float ms = base[(size_t)s * (vd + 2) + vd];
+    if (ms > -INFINITY) L += expf(ms - M) * base[(size_t)s * (vd + 2) + vd + 1];
+  }
+  const float inv = L > 0.f ? 1.0f / L : 0.f;
+  for (int d = threadIdx.x; d < vd; d += blockDim.x) {
+    float o = 0.f;
+    for (int s = 0; s < n_splits; ++s) {
+      const float ms = base[(size_t)s * (vd + 2) + vd];
+      if (ms > -INFINITY) o += expf(ms - M) * base[(size_t)s * (vd + 2) + d];
+    }
+    out[rh * vd + d] = from_f32<TO>(o * inv);
+  }
+}
+
+}  // namespace
+
+extern "C" int flint_qkv_write(const float* qkv, int n_partials, long long partial_stride, const float* bias,
+                               const int* pos, const int* slot, const float* cos_t, const float* sin_t, int rot,
+                               int interleaved, void* q_out, int q_dtype, void* k_cache, void* v_cache, int cache_dtype,
+                               const int* block_table, int max_pages, int page_size, int T, int nq, int nkv, int hd,
+                               int vd, float* v_keep, const float* v_from, float blend, int* status,
+                               cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (n_partials < 1) return fail("qkv_write: needs at least one partial");
+  if (rot < 0 || rot > hd || (rot & 1)) return fail("qkv_write: %d rotating dims do not fit head size %d", rot, hd);
+  if (page_size <= 0 || nq < 1 || nkv < 1 || hd < 1 || vd < 1) return fail("qkv_write: bad sizes");
+  const int W = (nq + nkv) * hd + nkv * vd;
+  const int threads = W >= 1024 ? 256 : 128;
+  FLINT_DISPATCH_DTYPE(q_dtype, TQ, FLINT_DISPATCH_DTYPE(cache_dtype, TC,
+      (launch_pdl(qkv_write_kernel<TQ, TC>, dim3(T), dim3(threads), 0, stream, qkv, n_partials, partial_stride, bias, pos,
+                  slot, cos_t, sin_t, rot, interleaved, (TQ*)q_out, (TC*)k_cache, (TC*)v_cache, block_table, max_pages,
+                  page_size, nq, nkv, hd, vd, v_keep, v_from, blend, status))));
+  return check_launch("qkv_write");
+}
+
+// `scratch` must hold T * nq * n_splits * (vd + 2) floats when n_splits > 1; split_keys * n_splits must cover the
+// most keys any row sees.
+extern "C" int flint_sink_attention(const void* q, int q_dtype, const void* k_cache, const void* v_cache, int cache_dtype,
+                                    const int* block_table, int max_pages, int page_size, const int* pos,
+                                    const int* slot, void* out, int T, int nq, int nkv, int hd, int vd, int window,
+                                    int keep_first, const float* sinks, float scale, int split_keys, int n_splits,
+                                    float* scratch, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (hd < 1 || vd < 1 || hd > 256 || vd > 32 * MAX_DPL)
+    return fail("sink_attention: head sizes %d (keys) and %d (values) are not supported (1 to 256)", hd, vd);
+  if (nkv <= 0 || nq % nkv) return fail("sink_attention: %d query heads do not divide into %d kv heads", nq, nkv);
+  if (n_splits < 1 || split_keys < 1) return fail("sink_attention: bad split (%d keys, %d splits)", split_keys, n_splits);
+  if (n_splits > 1 && !scratch) return fail("sink_attention: splits need scratch memory");
+  if (window < 0 || keep_first < 0) return fail("sink_attention: bad window");
+  const int elem = cache_dtype == FLINT_F32 ? 4 : 2;
+  if ((hd % 8) == 0 && (((uintptr_t)k_cache) & 15)) return fail("sink_attention: the key cache must start on 16 bytes");
+  (void)elem;
+  const int G = nq / nkv;
+  const int g_chunks = (G + GC - 1) / GC;
+  const long long items = (long long)T * nkv * g_chunks * n_splits;
+  const long long blocks = (items + WARPS - 1) / WARPS;
+  if (blocks > 0x7fffffffLL) return fail("sink_attention: too many work items");
+  const size_t smem = (size_t)WARPS * GC * hd * sizeof(float);
+#define LAUNCH(TQ, TC)                                                                                            \
+  launch_pdl(sink_attention_kernel<TQ, TC, TQ>, dim3((unsigned)blocks), dim3(WARPS * 32), smem, stream, (const TQ*)q, \
+             (const TC*)k_cache, (const TC*)v_cache, block_table, max_pages, page_size, pos, slot, (TQ*)out, scratch, T, \
+             nq, nkv, hd, vd, window, keep_first, sinks, scale, split_keys, n_splits, g_chunks)
+  FLINT_DISPATCH_DTYPE(q_dtype, TQ, FLINT_DISPATCH_DTYPE(cache_dtype, TC, LAUNCH(TQ, TC)));
+#undef LAUNCH
+  int rc = check_launch("sink_attention");
+  if (rc || n_splits == 1) return rc;
+  const int threads = vd >= 128 ? 128 : 64;
+  FLINT_DISPATCH_DTYPE(q_dtype, TO,
+      (launch_pdl(sink_combine_kernel<TO>, dim3((unsigned)((long long)T * nq)), dim3(threads), 0, stream,
+                  (const float*)scratch, (TO*)out, vd, n_splits, nq, sinks)));
+  return check_launch("sink_combine");
+}
+
+extern "C" const char* flint_attention_sink_last_error() { return g_error; }

@@ -436,7 +436,7 @@ extern "C" int flint_add_partials(float* x, const float* partials, int n_partial
 // rows that made them).
 template <typename TO>
 __global__ void gated_act_kernel(const float* __restrict__ p, int S, long long stride, TO* __restrict__ out,
-                                 int rows, int I, int act) {
+                                 int rows, int I, int act, float p0, float p1) {
   pdl_launch();
   pdl_wait();
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -448,20 +448,68 @@ __global__ void gated_act_kernel(const float* __restrict__ p, int S, long long s
     g += row[0];
     u += row[GATE_BLOCK];
   }
-  const float a = act == 0 ? g / (1.0f + expf(-g))
-                           : 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
-  out[i] = from_f32<TO>(a * u);
+  float y;
+  if (act == 2) {          // clamped: g = min(g, c), u = clamp(u, -c, c); g sigmoid(slope g) (u + 1); p0 = slope, p1 = c
+    g = fminf(g, p1);
+    u = fminf(fmaxf(u, -p1), p1);
+    y = g / (1.0f + expf(-p0 * g)) * (u + 1.0f);
+  } else {
+    const float a = act == 0 ? g / (1.0f + expf(-g))
+                             : 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
+    y = a * u;
+  }
+  out[i] = from_f32<TO>(y);
 }
 
 extern "C" int flint_gated_act(const float* partials, int S, long long stride, void* out, int out_dtype, int rows,
-                               int I, int act, cudaStream_t stream) {
+                               int I, int act, float p0, float p1, cudaStream_t stream) {
   const long long n = (long long)rows * I;
   if (n <= 0) return 0;
   if (S < 1) return fail("gated_act: needs at least one partial");
+  if (act < 0 || act > 2) return fail("gated_act: unknown activation %d", act);
   FLINT_DISPATCH_DTYPE(out_dtype, TO,
       launch_pdl(gated_act_kernel<TO>, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, partials, S, stride,
-                 (TO*)out, rows, I, act));
+                 (TO*)out, rows, I, act, p0, p1));
   return check_launch("gated_act");
+}
+
+// out[r, c] = act(scale_r * sum_z p[z][r, c]): the epilogue of an ungated product whose K range was split.  Without a
+// list every row has scale 1; with one, assignment a = (token, choice) names the row row_of[a] and its scale
+// row_scale[(a / top) * scale_stride + a % top] (a row no assignment names is left untouched).
+// act: 0 none, 1 gelu (erf), 2 gelu (tanh), 3 silu.
+template <typename TO>
+__global__ void row_act_kernel(const float* __restrict__ p, int S, long long stride, TO* __restrict__ out, int rows,
+                               int N, int act, const int* __restrict__ row_of, const float* __restrict__ row_scale,
+                               int top, int scale_stride) {
+  pdl_launch();
+  pdl_wait();
+  const int a = blockIdx.x;
+  const int r = row_of ? row_of[a] : a;
+  if (r < 0 || r >= rows) return;
+  const float sc = row_of ? row_scale[(size_t)(a / top) * scale_stride + a % top] : 1.0f;
+  for (int c = threadIdx.x; c < N; c += blockDim.x) {
+    float x = 0.f;
+    for (int z = 0; z < S; ++z) x += p[(size_t)z * stride + (size_t)r * N + c];
+    x *= sc;
+    float y = x;
+    if (act == 1) y = 0.5f * x * (1.0f + erff(x * 0.70710678118654752f));
+    else if (act == 2) y = 0.5f * x * (1.0f + tanhf(0.7978845608028654f * (x + 0.044715f * x * x * x)));
+    else if (act == 3) y = x / (1.0f + expf(-x));
+    out[(size_t)r * N + c] = from_f32<TO>(y);
+  }
+}
+
+extern "C" int flint_row_act(const float* partials, int S, long long stride, void* out, int out_dtype, int rows, int N,
+                             int act, const int* row_of, const float* row_scale, int top, int scale_stride,
+                             cudaStream_t stream) {
+  if (rows <= 0 || N <= 0) return 0;
+  if (S < 1) return fail("row_act: needs at least one partial");
+  if (act < 0 || act > 3) return fail("row_act: unknown activation %d", act);
+  if (row_of && (!row_scale || top < 1 || scale_stride < top)) return fail("row_act: a row list needs scales");
+  FLINT_DISPATCH_DTYPE(out_dtype, TO,
+      launch_pdl(row_act_kernel<TO>, dim3((unsigned)rows), dim3(N >= 1024 ? 256 : 128), 0, stream, partials, S, stride,
+                 (TO*)out, rows, N, act, row_of, row_scale, top, scale_stride));
+  return check_launch("row_act");
 }
 
 extern "C" const char* flint_elementwise_last_error() { return g_error; }

@@ -43,9 +43,11 @@ inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
 // ------------------------------------------------------------------------------------------------ pages
 // Pages of one layer group: a pool of page numbers with a LIFO free list (a page just freed is the next one
 // handed out, which keeps reuse frequent and easy to test) and one table per request slot.  Entries of a
-// table before first_live have been given back (window) and read NO_PAGE.
+// table before first_live have been given back (window) and read NO_PAGE, except the first kept_pages() of a
+// group whose window keeps a request's first positions: those stay until the request ends.
 struct Group {
   int n_pages, page_size, window, max_pages;
+  int keep_first = 0;               // with a window: the first so many positions of a request stay reachable
   std::vector<int> free_list;
   std::vector<char> held;
   std::vector<int> served;          // how many times each page was handed out
@@ -68,6 +70,8 @@ struct Group {
   int used_pages() const { return n_pages - (int)free_list.size(); }
   // the first position a query at pos can still see
   int first_visible(int pos) const { return window ? std::max(0, pos + 1 - window) : 0; }
+  // pages [0, kept_pages()) hold positions that every later query still sees
+  int kept_pages() const { return window ? ceil_div(keep_first, page_size) : 0; }
 
   int take() {
     if (free_list.empty()) return fail(E_CACHE, "page pool exhausted");
@@ -99,8 +103,11 @@ struct Group {
   int pages_needed(int slot, int start, int end) const {
     const Table& t = tables[slot];
     const int want_hi = ceil_div(end, page_size);
-    const int lo = std::max((int)t.pages.size(), first_visible(start) / page_size);
-    return std::max(0, want_hi - lo);
+    const int have = (int)t.pages.size();
+    const int lo = std::max(have, first_visible(start) / page_size);
+    // beside the pages from the window's start on, the kept first pages that do not exist yet
+    const int kept = std::max(0, std::min(std::min(kept_pages(), want_hi), lo) - have);
+    return std::max(0, want_hi - lo) + kept;
   }
   // make pages exist for positions [first_visible(start), end)
   int ensure(int slot, int start, int end) {
@@ -113,7 +120,7 @@ struct Group {
     bool changed = false;
     while ((int)t.pages.size() < want_hi) {
       const int i = (int)t.pages.size();
-      if (i < first) {
+      if (i < first && i >= kept_pages()) {
         t.pages.push_back(NO_PAGE);      // never needed: behind the window from the start
         t.first_live = std::max(t.first_live, i + 1);
       } else {
@@ -132,7 +139,7 @@ struct Group {
     Table& t = tables[slot];
     const int dead_hi = std::min(first_visible(next_pos) / page_size, (int)t.pages.size());
     int n = 0;
-    for (int i = t.first_live; i < dead_hi; ++i)
+    for (int i = std::max(t.first_live, kept_pages()); i < dead_hi; ++i)
       if (t.pages[i] != NO_PAGE) {
         if (int rc = give_back(t.pages[i])) return rc;
         t.pages[i] = NO_PAGE;
@@ -564,6 +571,12 @@ void* flint_rt_group_create(int n_pages, int page_size, int window, int max_slot
   return new Group(n_pages, page_size, window, max_slots, max_pages_per_request, host_table);
 }
 void flint_rt_group_destroy(void* g) { delete (Group*)g; }
+// with a window: the first `n` positions of every request stay reachable (set before any request is admitted)
+int flint_rt_group_set_keep_first(void* g, int n) {
+  if (n < 0) return fail(E_CACHE, "keep_first must not be negative, got %d", n);
+  ((Group*)g)->keep_first = n;
+  return 0;
+}
 int flint_rt_group_take(void* g) { return ((Group*)g)->take(); }
 int flint_rt_group_give_back(void* g, int page) { return ((Group*)g)->give_back(page); }
 int flint_rt_group_free_pages(void* g) { return ((Group*)g)->free_pages(); }

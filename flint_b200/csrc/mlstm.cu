@@ -1,0 +1,212 @@
+// The mLSTM matrix memory as a recurrence over the tokens of a step, in float32.
+//
+// Per head, with log gates i and f, a running maximum m (from 0), S [D, V] and n [D] (from 0):
+//   m' = max(f + m, i);  S' = e^(f + m - m') S + e^(i - m') k v^T;  n' = e^(f + m - m') n + e^(i - m') k;
+//   o  = S'^T q / (max(|n' . q|, e^(-m')) + 1e-6)
+//
+// Three kernels.  flint_mlstm_prepare adds up the partial sums of the input projection [q | k | v | g | z_i | z_f]
+// and turns them into what the recurrence reads: q times D^(-1/2), i = cap tanh((z_i + b_i) / cap),
+// f = logsigmoid(cap tanh((z_f + b_f) / cap)); it is parallel over tokens.  flint_mlstm_scan walks the tokens of
+// every request in order: a warp owns CW columns of one head's S (lane l holds rows l, l + 32, ... of each) and a
+// copy of n and m, so no warp waits for another; the next token's operands are fetched while the current one is
+// worked.  The state is read from and written back to the request's row of the state slab
+// (per head: S transposed [V, D], then n [D], then m), so a prompt cut anywhere gives the same numbers.
+// flint_mlstm_finish divides each head's o by its root mean square and applies the scale and the output gate.
+//
+// The reference has no mLSTM; its recurrent family keeps state per sequence slot in the same way
+// (crates/thuban_architectures/src/qwen35/state.rs:5-55).
+#include <math.h>
+#include <stdarg.h>
+#include "common.cuh"
+
+using namespace flint;
+
+namespace {
+
+constexpr int CW = 4;          // columns of S per warp
+constexpr int SCAN_WARPS = 4;  // warps per block of the scan
+
+__device__ __forceinline__ float log_sigmoid(float z) { return fminf(z, 0.f) - log1pf(expf(-fabsf(z))); }
+
+// x[t, c] = f(sum_z partials[z][t, c]); N = 2 H D + 2 H V + 2 H columns
+__global__ void mlstm_prepare_kernel(const float* __restrict__ partials, int S, long long stride,
+                                     const float* __restrict__ b_gates, float* __restrict__ x, long long n, int N,
+                                     int H, int D, int V, float cap, float q_scale) {
+  pdl_launch();
+  pdl_wait();
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const int c = (int)(i % N);
+  float v = 0.f;
+  for (int z = 0; z < S; ++z) v += partials[(size_t)z * stride + i];
+  const int gates0 = 2 * H * D + 2 * H * V;
+  if (c < H * D) {
+    v *= q_scale;
+  } else if (c >= gates0) {
+    const float z = cap * tanhf((v + b_gates[c - gates0]) / cap);
+    v = c < gates0 + H ? z : log_sigmoid(z);
+  }
+  x[i] = v;
+}
+
+template <int ND>
+__global__ void __launch_bounds__(SCAN_WARPS * 32)
+mlstm_scan_kernel(const float* __restrict__ x, int N, const int* __restrict__ slot, const int* __restrict__ seq_start,
+                  int n_seq, float* __restrict__ state, long long state_stride, float* __restrict__ out, int H, int D,
+                  int V, int col_groups) {
+  pdl_launch();
+  pdl_wait();
+  const int lane = threadIdx.x & 31;
+  const long long item = (long long)blockIdx.x * SCAN_WARPS + (threadIdx.x >> 5);
+  if (item >= (long long)n_seq * H * col_groups) return;
+  const int cg = (int)(item % col_groups), h = (int)((item / col_groups) % H), e = (int)(item / ((long long)col_groups * H));
+  const int t0 = seq_start ? seq_start[e] : e, t1 = seq_start ? seq_start[e + 1] : e + 1;
+  if (t1 <= t0) return;
+  float* st = state + (size_t)slot[t0] * state_stride + (size_t)h * ((size_t)D * V + D + 1);
+  const int c0 = cg * CW;
+  float Sm[CW][ND], nv[ND];
+#pragma unroll
+  for (int i = 0; i < ND; ++i) {
+    const int d = lane + 32 * i;
+    nv[i] = d < D ? st[(size_t)D * V + d] : 0.f;
+#pragma unroll
+    for (int c = 0; c < CW; ++c) Sm[c][i] = (d < D && c0 + c < V) ? st[(size_t)(c0 + c) * D + d] : 0.f;
+  }
+  float m = st[(size_t)D * V + D];
+  const int oq = h * D, ok = H * D + h * D, ov = 2 * H * D + h * V + c0, oi = 2 * H * D + 2 * H * V + h;
+  float q[ND], k[ND], v[CW], gi, gf;
+  auto fetch = [&](int t, float* qq, float* kk, float* vv, float& ii, float& ff) {
+    const float* row = x + (size_t)t * N;
+#pragma unroll
+    for (int i = 0; i < ND; ++i) {
+      const int d = lane + 32 * i;
+      qq[i] = d < D ? row[oq + d] : 0.f;
+      kk[i] = d < D ? row[ok + d] : 0.f;
+    }
+#pragma unroll
+    for (int c = 0; c < CW; ++c) vv[c] = c0 + c < V ? row[ov + c] : 0.f;
+    ii = row[oi];
+    ff = row[oi + H];
+  };
+  fetch(t0, q, k, v, gi, gf);
+  for (int t = t0; t < t1; ++t) {
+    float qn[ND], kn[ND], vn[CW], gin = 0.f, gfn = 0.f;
+    if (t + 1 < t1) fetch(t + 1, qn, kn, vn, gin, gfn);
+    const float m_new = fmaxf(gf + m, gi);
+    const float a = expf(gf + m - m_new), b = expf(gi - m_new);
+    float nq = 0.f, acc[CW];
+#pragma unroll
+    for (int c = 0; c < CW; ++c) acc[c] = 0.f;
+#pragma unroll
+    for (int i = 0; i < ND; ++i) {
+      const float bk = b * k[i];
+      nv[i] = fmaf(a, nv[i], bk);
+      nq = fmaf(nv[i], q[i], nq);
+#pragma unroll
+      for (int c = 0; c < CW; ++c) {
+        Sm[c][i] = fmaf(a, Sm[c][i], bk * v[c]);
+        acc[c] = fmaf(Sm[c][i], q[i], acc[c]);
+      }
+    }
+    nq = warp_sum(nq);
+#pragma unroll
+    for (int c = 0; c < CW; ++c) acc[c] = warp_sum(acc[c]);
+    const float den = fmaxf(fabsf(nq), expf(-m_new)) + 1e-6f;
+    float mine = acc[0];
+#pragma unroll
+    for (int c = 1; c < CW; ++c) mine = lane == c ? acc[c] : mine;
+    if (lane < CW && c0 + lane < V) out[((size_t)t * H + h) * V + c0 + lane] = mine / den;
+    m = m_new;
+    if (t + 1 < t1) {
+#pragma unroll
+      for (int i = 0; i < ND; ++i) { q[i] = qn[i]; k[i] = kn[i]; }
+#pragma unroll
+      for (int c = 0; c < CW; ++c) v[c] = vn[c];
+      gi = gin;
+      gf = gfn;
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < ND; ++i) {
+    const int d = lane + 32 * i;
+    if (d < D) {
+      if (cg == 0) st[(size_t)D * V + d] = nv[i];
+#pragma unroll
+      for (int c = 0; c < CW; ++c)
+        if (c0 + c < V) st[(size_t)(c0 + c) * D + d] = Sm[c][i];
+    }
+  }
+  if (cg == 0 && lane == 0) st[(size_t)D * V + D] = m;
+}
+
+// out[t, h, c] = o[t, h, c] / sqrt(mean_c o[t, h, :]^2 + eps) * w[h V + c] * sigmoid(gate[t, h V + c]); a warp per (t, h)
+template <typename TO>
+__global__ void mlstm_finish_kernel(const float* __restrict__ o, const float* __restrict__ gate, long long gate_stride,
+                                    const float* __restrict__ w, float eps, TO* __restrict__ out, long long n_items,
+                                    int H, int V) {
+  pdl_launch();
+  pdl_wait();
+  const int lane = threadIdx.x & 31;
+  const long long item = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (item >= n_items) return;
+  const long long t = item / H;
+  const int h = (int)(item % H);
+  const float* row = o + ((size_t)t * H + h) * V;
+  float ss = 0.f;
+  for (int c = lane; c < V; c += 32) ss = fmaf(row[c], row[c], ss);
+  ss = warp_sum(ss);
+  const float inv = 1.0f / sqrtf(ss / (float)V + eps);
+  for (int c = lane; c < V; c += 32) {
+    const float g = gate[(size_t)t * gate_stride + (size_t)h * V + c];
+    out[((size_t)t * H + h) * V + c] = from_f32<TO>(row[c] * inv * w[(size_t)h * V + c] * (1.0f / (1.0f + expf(-g))));
+  }
+}
+
+}  // namespace
+
+// partials [S, T, N] float32 -> x [T, N] float32 (see the top of the file); N = 2 H D + 2 H V + 2 H.
+extern "C" int flint_mlstm_prepare(const float* partials, int S, long long stride, const float* b_gates, float* x,
+                                   int T, int H, int D, int V, float cap, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (S < 1) return fail("mlstm_prepare: needs at least one partial");
+  if (H < 1 || D < 1 || V < 1 || !(cap > 0.f)) return fail("mlstm_prepare: bad sizes (%d heads, %d, %d) or gate cap", H, D, V);
+  const int N = 2 * H * D + 2 * H * V + 2 * H;
+  const long long n = (long long)T * N;
+  launch_pdl(mlstm_prepare_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, partials, S, stride, b_gates,
+             x, n, N, H, D, V, cap, 1.0f / sqrtf((float)D));
+  return check_launch("mlstm_prepare");
+}
+
+// x [T, N] as flint_mlstm_prepare leaves it; the rows of request e are seq_start[e] .. seq_start[e + 1] - 1 (NULL:
+// row e alone); state [slots, state_stride] float32; out [T, H V] float32.
+extern "C" int flint_mlstm_scan(const float* x, const int* slot, const int* seq_start, int n_seq, float* state,
+                                long long state_stride, float* out, int T, int H, int D, int V, cudaStream_t stream) {
+  if (T <= 0 || n_seq <= 0) return 0;
+  if (H < 1 || D < 1 || V < 1 || D > 256) return fail("mlstm_scan: %d heads of %d x %d are not supported (dims up to 256)", H, D, V);
+  if (state_stride < (long long)H * ((long long)D * V + D + 1)) return fail("mlstm_scan: the state rows are too short");
+  if (!seq_start && n_seq != T) return fail("mlstm_scan: without a list of starts every request brings one row");
+  const int N = 2 * H * D + 2 * H * V + 2 * H;
+  const int col_groups = (V + CW - 1) / CW;
+  const long long items = (long long)n_seq * H * col_groups;
+  const dim3 grid((unsigned)((items + SCAN_WARPS - 1) / SCAN_WARPS)), block(SCAN_WARPS * 32);
+#define SCAN(ND) launch_pdl(mlstm_scan_kernel<ND>, grid, block, 0, stream, x, N, slot, seq_start, n_seq, state, \
+                            state_stride, out, H, D, V, col_groups)
+  if (D <= 32) SCAN(1);
+  else if (D <= 64) SCAN(2);
+  else if (D <= 128) SCAN(4);
+  else SCAN(8);
+#undef SCAN
+  return check_launch("mlstm_scan");
+}
+
+extern "C" int flint_mlstm_finish(const float* o, const float* gate, long long gate_stride, const float* w, float eps,
+                                  void* out, int out_dtype, int T, int H, int V, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  const long long items = (long long)T * H;
+  FLINT_DISPATCH_DTYPE(out_dtype, TO,
+      launch_pdl(mlstm_finish_kernel<TO>, dim3((unsigned)((items + 3) / 4)), dim3(128), 0, stream, o, gate, gate_stride, w,
+                 eps, (TO*)out, items, H, V));
+  return check_launch("mlstm_finish");
+}
+
+extern "C" const char* flint_mlstm_last_error() { return g_error; }

@@ -342,6 +342,89 @@ extern "C" int flint_router_topk(const float* x, const void* wr, int w_dtype, in
 }
 
 // Upper bound of row tiles for n_assign rows over E experts.
+// --------------------------------------------------------------------------- sigmoid router
+// Scores s_e = sigmoid(<x, Wr[e]>) in float32 over the first E rows of Wr; the `top` largest are chosen (the lower
+// index among equals) with their scores as they are.  Rows E .. E + X - 1 of Wr are not experts but gates of
+// always-on parts: their sigmoids go to weights[:, top:], and weights[:, :top] is 1 (the chosen experts' scores
+// scale their inputs, so their outputs are added as they are).  A warp takes RT tokens and reads every weight
+// row once for all of them.
+constexpr int RT = 4;
+template <typename TW>
+__global__ void __launch_bounds__(128)
+router_sigmoid_kernel(const float* __restrict__ x, const TW* __restrict__ wr, int T, int H, int E, int X, int top,
+                      int* __restrict__ expert_ids, float* __restrict__ scores, float* __restrict__ weights,
+                      float* __restrict__ logits_out) {
+  extern __shared__ float smem[];            // per warp: RT * (E + X) logits
+  pdl_launch();
+  pdl_wait();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t0 = (blockIdx.x * 4 + warp) * RT;
+  if (t0 >= T) return;
+  const int nt = min(RT, T - t0), R = E + X;
+  float* z = smem + warp * RT * R;
+  for (int e = 0; e < R; ++e) {
+    float acc[RT];
+#pragma unroll
+    for (int r = 0; r < RT; ++r) acc[r] = 0.f;
+    const TW* w = wr + (size_t)e * H;
+    for (int d = lane; d < H; d += 32) {
+      const float wv = to_f32(w[d]);
+#pragma unroll
+      for (int r = 0; r < RT; ++r)
+        if (r < nt) acc[r] = fmaf(x[(size_t)(t0 + r) * H + d], wv, acc[r]);
+    }
+#pragma unroll
+    for (int r = 0; r < RT; ++r) {
+      const float v = warp_sum(acc[r]);
+      if (lane == 0 && r < nt) z[r * R + e] = v;
+    }
+  }
+  __syncwarp();
+  for (int r = 0; r < nt; ++r) {
+    const int t = t0 + r;
+    float* zr = z + r * R;
+    if (logits_out)
+      for (int e = lane; e < R; e += 32) logits_out[(size_t)t * R + e] = zr[e];
+    __syncwarp();
+    for (int e = lane; e < R; e += 32) zr[e] = 1.0f / (1.0f + expf(-zr[e]));
+    __syncwarp();
+    for (int c = 0; c < top; ++c) {
+      float val = -1.f;
+      int idx = 0x7fffffff;
+      for (int e = lane; e < E; e += 32)
+        if (zr[e] > val) { val = zr[e]; idx = e; }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, val, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+        if (ov > val || (ov == val && oi < idx)) { val = ov; idx = oi; }
+      }
+      if (lane == 0) {
+        expert_ids[(size_t)t * top + c] = idx;
+        scores[(size_t)t * top + c] = val;
+        weights[(size_t)t * (top + X) + c] = 1.0f;
+        zr[idx] = -2.f;                       // taken
+      }
+      __syncwarp();
+    }
+    for (int e = lane; e < X; e += 32) weights[(size_t)t * (top + X) + top + e] = zr[E + e];
+  }
+}
+
+extern "C" int flint_router_sigmoid(const float* x, const void* wr, int w_dtype, int E, int X, int top, int* expert_ids,
+                                    float* scores, float* weights, float* logits_out, int T, int H,
+                                    cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (E < 1 || X < 0 || top < 1 || top > E) return fail("router_sigmoid: %d of %d experts (+%d gates) is not supported", top, E, X);
+  const size_t smem = (size_t)4 * RT * (E + X) * sizeof(float);
+  if (smem > 48 * 1024) return fail("router_sigmoid: too many experts (%d)", E);
+  const unsigned blocks = (unsigned)((T + 4 * RT - 1) / (4 * RT));
+  FLINT_DISPATCH_DTYPE(w_dtype, TW,
+      launch_pdl(router_sigmoid_kernel<TW>, dim3(blocks), dim3(128), smem, stream, x, (const TW*)wr, T, H, E, X, top,
+                 expert_ids, scores, weights, logits_out));
+  return check_launch("router_sigmoid");
+}
+
 extern "C" int flint_moe_max_tiles(int n_assign, int E, int tile_rows) {
   return n_assign / tile_rows + (E < n_assign ? E : n_assign);
 }

@@ -369,10 +369,48 @@ class CudaOps:
             flat[..., half, :, :] = w.reshape(*lead, blocks, b, k)
         return out.view(*lead, 2 * blocks * b, k)
 
-    def gated_gemm(self, x, w13, out, act="silu", plan: MoePlan | None = None):
+    def gated_gemm(self, x, w13, out, act="silu", plan: MoePlan | None = None, act_params=None):
         """out = act(x @ Wg.T) * (x @ Wu.T); w13 = pair_gate_up(Wg, Wu): [paired_rows(N), K], or with a
-        plan (rows grouped by expert) [E, paired_rows(N), K]."""
+        plan (rows grouped by expert) [E, paired_rows(N), K].  act "swish_clamped" with act_params (slope, limit):
+        g = min(gate, limit), u = clamp(up, -limit, limit), out = g sigmoid(slope g) (u + 1); it runs as a plain
+        product over the paired rows and an activation kernel over its float32 sums."""
+        if act == "swish_clamped":
+            if act_params is None or plan is not None:
+                raise KernelError("gated_gemm: swish_clamped takes (slope, limit) and no plan")
+            _check(out, "out", dims=2)
+            M, N = out.shape
+            if w13.dim() != 2 or w13.shape[0] != self.paired_rows(N) or w13.shape[1] != x.shape[1] or x.shape[0] != M:
+                raise KernelError("gated_gemm: shapes do not match")
+            parts = self.gemm_partials(x, w13)
+            return self._run("elementwise", "flint_gated_act", _ptr(parts), c_int(parts.shape[0]), c_longlong(parts.stride(0)),
+                             _ptr(out), c_int(_code(out.dtype)), c_int(M), c_int(N), c_int(2), c_float(act_params[0]),
+                             c_float(act_params[1]))
         self._gemm(x, w13, True, out, None, False, act, plan)
+
+    ROW_ACTS = {"none": 0, "gelu": 1, "gelu_pytorch_tanh": 2, "silu": 3}
+
+    def row_act(self, partials, out, act, row_of=None, row_scale=None):
+        """out[r] = act(scale_r * sum_z partials[z][r]): partials [S, rows, N] float32 (an ungated product left as
+        partial sums).  With ``row_of`` [T, top] (the row of every (token, choice)) and ``row_scale`` [T, >= top], row
+        row_of[t, c] is scaled by row_scale[t, c] before the activation; else every row by 1."""
+        if partials.dim() == 2:
+            partials = partials.unsqueeze(0)
+        _check(partials, "partials", torch.float32, 3)
+        _check(out, "out", dims=2)
+        S, rows, N = partials.shape
+        if tuple(out.shape) != (rows, N) or act not in self.ROW_ACTS:
+            raise KernelError(f"row_act: output {tuple(out.shape)} or activation {act!r} does not fit")
+        top = stride = 0
+        n_launch = rows
+        if row_of is not None:
+            _check(row_of, "row_of", torch.int32, 2)
+            _check(row_scale, "row_scale", torch.float32, 2)
+            top, stride = row_of.shape[1], row_scale.stride(0)
+            if row_of.numel() != rows or row_scale.shape[0] != row_of.shape[0] or row_scale.shape[1] < top:
+                raise KernelError("row_act: the row list does not match the rows")
+        self._run("elementwise", "flint_row_act", _ptr(partials), c_int(S), c_longlong(partials.stride(0)), _ptr(out),
+                  c_int(_code(out.dtype)), c_int(n_launch), c_int(N), c_int(self.ROW_ACTS[act]), _ptr(row_of), _ptr(row_scale),
+                  c_int(top), c_int(stride))
 
     def grouped_gemm(self, x, w, out, plan: MoePlan, plan_ready=False):
         """out[r] = x[r] @ w[expert of row r].T; w [E, N, K].  ``plan_ready``: another product over the same plan
@@ -461,7 +499,7 @@ class CudaOps:
                 parts = self.gemm_partials(x, w, plan=plan)
                 self._run("elementwise", "flint_gated_act", _ptr(parts), c_int(parts.shape[0]),
                           c_longlong(parts.stride(0)), _ptr(out), c_int(_code(out.dtype)), c_int(M), c_int(N),
-                          c_int(act_code))
+                          c_int(act_code), c_float(0.0), c_float(0.0))
                 return
             self._gemm_tc(x, w, gated, out, bias, accumulate, act_code, plan, M, N, K, plan_ready)
         else:
@@ -701,6 +739,125 @@ class CudaOps:
                   c_int(nq), c_int(nkv), c_int(hd), c_int(window), c_float(scale), c_int(split_keys), c_int(n_splits),
                   _ptr(scratch), _ptr(rows))
 
+    # ------------------------------------------------------------------ attention with kept first tokens and a sink
+    def qkv_write(self, qkv, bias, pos, slot, cos, sin, rot, style, q_out, cache, nq, nkv, hd, vd, status,
+                  v_keep=None, v_from=None, blend=0.0):
+        """qkv [S, T, W] float32 (partial sums of the q/k/v projection, W = (nq + nkv) hd + nkv vd) plus ``bias``:
+        q (the leading ``rot`` dims of every head rotated by the row's position) goes to q_out [T, nq hd], keys
+        (rotated alike) and values into the row's cache page.  ``v_keep`` [T, nkv vd] float32 receives the values
+        as projected; with ``v_from`` (same shape) the cached values are (1 - blend) v + blend v_from."""
+        if style not in ("half", "interleaved"):
+            raise KernelError(f"qkv_write: unknown rotation style {style!r}")
+        if qkv.dim() == 2:
+            qkv = qkv.unsqueeze(0)
+        _check(qkv, "qkv", torch.float32, 3)
+        S, T, W = qkv.shape
+        if W != (nq + nkv) * hd + nkv * vd:
+            raise KernelError("qkv_write: the projection's width does not match the head counts")
+        if bias is not None and (bias.dtype != torch.float32 or bias.numel() != W):
+            raise KernelError("qkv_write: bias must be float32 of the projection's width")
+        _check(q_out, "q_out", dims=2)
+        if tuple(q_out.shape) != (T, nq * hd):
+            raise KernelError(f"qkv_write: q_out must be [{T}, {nq * hd}]")
+        _check(cos, "cos", torch.float32, 2)
+        _check(sin, "sin", torch.float32, 2)
+        if rot and cos.shape[1] * 2 != rot:
+            raise KernelError("qkv_write: table width must be rot/2")
+        k, v, bt, P = cache.k, cache.v, cache.block_table, cache.page_size
+        if tuple(k.shape[1:]) != (nkv, P, hd) or tuple(v.shape[1:]) != (nkv, P, vd) or v.dtype != k.dtype:
+            raise KernelError(f"qkv_write: cache pages are {tuple(k.shape[1:])} and {tuple(v.shape[1:])}, expected "
+                              f"{(nkv, P, hd)} and {(nkv, P, vd)}")
+        for name, t in (("v_keep", v_keep), ("v_from", v_from)):
+            if t is not None:
+                _check(t, name, torch.float32, 2)
+                if tuple(t.shape) != (T, nkv * vd):
+                    raise KernelError(f"qkv_write: {name} must be [{T}, {nkv * vd}]")
+        self._run("attention_sink", "flint_qkv_write", _ptr(qkv), c_int(S), c_longlong(qkv.stride(0)), _ptr(bias), _ptr(pos),
+                  _ptr(slot), _ptr(cos), _ptr(sin), c_int(rot), c_int(1 if style == "interleaved" else 0), _ptr(q_out),
+                  c_int(_code(q_out.dtype)), _ptr(k), _ptr(v), c_int(_code(k.dtype)), _ptr(bt), c_int(bt.shape[1]), c_int(P),
+                  c_int(T), c_int(nq), c_int(nkv), c_int(hd), c_int(vd), _ptr(v_keep), _ptr(v_from), c_float(blend),
+                  _ptr(status))
+
+    def sink_attention_plan(self, T, nq, nkv, span):
+        """(keys per split, splits): enough warps to fill the device, at least 64 keys each."""
+        base = T * nkv * -(-(nq // nkv) // 4)
+        span = max(span, 1)
+        n = max(1, min(-(-span // 64), -(-8 * self.sm_count // base)))
+        keys = -(-(-(-span // n)) // 32) * 32
+        return keys, -(-span // keys)
+
+    def sink_attention(self, q, cache, step, out, nq, nkv, hd, vd, window, keep_first, sinks, scale, splits=None):
+        """Every row over its request's cached keys [.., hd] and values [.., vd]: row at position p sees key j if
+        j <= p and (p - j < window or j < keep_first) (window 0: all); ``sinks`` [nq] float32 (or None): a logit
+        per query head that joins the softmax's denominator.  q [T, nq hd] -> out [T, nq vd]."""
+        _check(q, "q", dims=2)
+        _check(out, "out", q.dtype, 2)
+        T = q.shape[0]
+        P = cache.page_size
+        if q.shape[1] != nq * hd or tuple(out.shape) != (T, nq * vd):
+            raise KernelError("sink_attention: q/out width does not match the head counts")
+        if tuple(cache.k.shape[1:]) != (nkv, P, hd) or tuple(cache.v.shape[1:]) != (nkv, P, vd):
+            raise KernelError("sink_attention: cache pages do not match the head counts")
+        if sinks is not None:
+            _check(sinks, "sinks", torch.float32, 1)
+            if sinks.numel() != nq:
+                raise KernelError(f"sink_attention: sinks must have {nq} entries")
+        span = min(step.max_kv_len, window + keep_first) if window else step.max_kv_len
+        keys, n = splits if splits is not None else self.sink_attention_plan(T, nq, nkv, span)
+        if keys * n < span:
+            raise KernelError(f"sink_attention: {n} splits of {keys} keys do not cover {span} keys")
+        scratch = torch.empty(T * nq * n * (vd + 2), dtype=torch.float32, device=q.device) if n > 1 else None
+        self._run("attention_sink", "flint_sink_attention", _ptr(q), c_int(_code(q.dtype)), _ptr(cache.k), _ptr(cache.v),
+                  c_int(_code(cache.k.dtype)), _ptr(cache.block_table), c_int(cache.block_table.shape[1]), c_int(P),
+                  _ptr(step.pos), _ptr(step.slot), _ptr(out), c_int(T), c_int(nq), c_int(nkv), c_int(hd), c_int(vd),
+                  c_int(window), c_int(keep_first), _ptr(sinks), c_float(scale), c_int(keys), c_int(n), _ptr(scratch))
+
+    # ------------------------------------------------------------------ matrix memory (mLSTM)
+    def mlstm_scan(self, proj, b_gates, slot, seq_start, n_seq, state, out, H, D, V, cap):
+        """proj [S, T, N] float32: partial sums of the projection [q | k | v | g | z_i | z_f] (N = 2 H D + 2 H V +
+        2 H); b_gates [2 H]: the gates' biases.  Runs the recurrence over every request's rows in order (request e
+        owns rows seq_start[e] .. seq_start[e + 1] - 1; ``seq_start`` None: row e alone), from and into ``state``
+        [slots, H (D V + D + 1)] float32, and writes the heads' unnormalised outputs to out [T, H V] float32.
+        Returns the output gate's pre-activations, a [T, H V] view."""
+        if proj.dim() == 2:
+            proj = proj.unsqueeze(0)
+        _check(proj, "proj", torch.float32, 3)
+        S, T, N = proj.shape
+        if N != 2 * H * D + 2 * H * V + 2 * H:
+            raise KernelError("mlstm_scan: the projection's width does not match the sizes")
+        _check(b_gates, "b_gates", torch.float32, 1)
+        _check(state, "state", torch.float32, 2)
+        _check(out, "out", torch.float32, 2)
+        if b_gates.numel() != 2 * H or tuple(out.shape) != (T, H * V) or state.shape[1] < H * (D * V + D + 1):
+            raise KernelError("mlstm_scan: shapes do not match")
+        if seq_start is not None:
+            _check(seq_start, "seq_start", torch.int32, 1)
+            if seq_start.numel() != n_seq + 1:
+                raise KernelError("mlstm_scan: seq_start must have one entry more than there are requests")
+        elif n_seq != T:
+            raise KernelError("mlstm_scan: without seq_start every request brings one row")
+        x = torch.empty((T, N), dtype=torch.float32, device=proj.device)
+        self._run("mlstm", "flint_mlstm_prepare", _ptr(proj), c_int(S), c_longlong(proj.stride(0)), _ptr(b_gates), _ptr(x),
+                  c_int(T), c_int(H), c_int(D), c_int(V), c_float(cap))
+        self._run("mlstm", "flint_mlstm_scan", _ptr(x), _ptr(slot), _ptr(seq_start), c_int(n_seq), _ptr(state),
+                  c_longlong(state.stride(0)), _ptr(out), c_int(T), c_int(H), c_int(D), c_int(V))
+        g0 = 2 * H * D + H * V
+        return x[:, g0:g0 + H * V]
+
+    def mlstm_finish(self, o, gate, norm_w, eps, out, H, V):
+        """out[t, h] = o[t, h] / rms(o[t, h]) * norm_w[h] * sigmoid(gate[t, h]): o [T, H V] float32, gate a
+        [T, H V] float32 view (rows may be strided), norm_w [H V] float32."""
+        _check(o, "o", torch.float32, 2)
+        _check(gate, "gate", torch.float32, 2, contiguous=False)
+        _check(norm_w, "norm_w", torch.float32, 1)
+        _check(out, "out", dims=2)
+        T = o.shape[0]
+        if o.shape[1] != H * V or tuple(gate.shape) != (T, H * V) or gate.stride(1) != 1 or norm_w.numel() != H * V \
+                or tuple(out.shape) != (T, H * V):
+            raise KernelError("mlstm_finish: shapes do not match")
+        self._run("mlstm", "flint_mlstm_finish", _ptr(o), _ptr(gate), c_longlong(gate.stride(0)), _ptr(norm_w), c_float(eps),
+                  _ptr(out), c_int(_code(out.dtype)), c_int(T), c_int(H), c_int(V))
+
     # ------------------------------------------------------------------ attention over a cached latent
     def head_products(self, x, w, out):
         """A small product per head: out[t, h, :] = w[h] @ x[t, h, :].  x [T, H, K], w [H, N, K], out [T, H, N]; x and
@@ -877,6 +1034,28 @@ class CudaOps:
             _check(logits_out, "router logits", torch.float32, 2)
         self._run("moe", "flint_router_topk", _ptr(x), _ptr(wr), c_int(_code(wr.dtype)), c_int(top), c_int(n_groups),
                   c_int(keep), c_float(scale), _ptr(expert_ids), _ptr(gates), _ptr(logits_out), c_int(T), c_int(H), c_int(E))
+
+    def router_sigmoid(self, x, wr, E, top, expert_ids, scores, weights, logits_out=None):
+        """Sigmoid router: scores sigmoid(x @ wr[:E].T) in float32, the ``top`` largest chosen (the lower index among
+        equals), expert_ids and scores [T, top].  Rows of wr beyond E are gates of always-on parts: weights
+        [T, top + X] gets 1 for the chosen experts and the sigmoids of those rows after them."""
+        _check(x, "x", torch.float32, 2)
+        _check(wr, "router weight", dims=2)
+        T, H = x.shape
+        X = wr.shape[0] - E
+        if wr.shape[1] != H or X < 0:
+            raise KernelError("router: weight shape does not match")
+        _check(expert_ids, "expert_ids", torch.int32, 2)
+        _check(scores, "scores", torch.float32, 2)
+        _check(weights, "weights", torch.float32, 2)
+        if tuple(expert_ids.shape) != (T, top) or tuple(scores.shape) != (T, top) or tuple(weights.shape) != (T, top + X):
+            raise KernelError(f"router: choices and scores must be [{T}, {top}], weights [{T}, {top + X}]")
+        if logits_out is not None:
+            _check(logits_out, "router logits", torch.float32, 2)
+            if tuple(logits_out.shape) != (T, E + X):
+                raise KernelError(f"router: logits must be [{T}, {E + X}]")
+        self._run("moe", "flint_router_sigmoid", _ptr(x), _ptr(wr), c_int(_code(wr.dtype)), c_int(E), c_int(X), c_int(top),
+                  _ptr(expert_ids), _ptr(scores), _ptr(weights), _ptr(logits_out), c_int(T), c_int(H))
 
     def _plan_buffers(self, expert_ids, n_experts, tile_rows):
         _check(expert_ids, "expert_ids", torch.int32, 2)

@@ -19,6 +19,7 @@ _lib = None
 _SIGNATURES = {
     "flint_rt_last_error": (c_char_p, []),
     "flint_rt_group_create": (c_void_p, [c_int, c_int, c_int, c_int, c_int, c_void_p]),
+    "flint_rt_group_set_keep_first": (c_int, [c_void_p, c_int]),
     "flint_rt_group_destroy": (None, [c_void_p]),
     "flint_rt_group_take": (c_int, [c_void_p]),
     "flint_rt_group_give_back": (c_int, [c_void_p, c_int]),

@@ -75,6 +75,7 @@ class StepContext:
     even_lengths: bool = False  # a decode batch whose requests are about equally long (set by the caller)
     record: dict | None = None  # filled by parts when a test asks for internals
     plans: dict = field(default_factory=dict)     # what mixers worked out for this step (Mixer.plan_step), by kind
+    shared: dict = field(default_factory=dict)    # tensors a layer leaves for later layers of the same step, by name
 
     def tiling(self, needs: StepNeeds) -> Tiling:
         try:

@@ -17,6 +17,7 @@ from ..cache.manager import KVSpec
 from ..engine.step import StepNeeds
 from ..errors import ConfigError, ModelError
 from ..registry import MIXERS, POSITION_ENCODINGS
+from ..weights.sources import WeightSpec
 from .base import Mixer, Pending, mat, matmul_dtype, vec
 
 
@@ -31,7 +32,15 @@ def shared_position_encoding(spec, ctx):
 @MIXERS.register("attention")
 class Attention(Mixer):
     """params: hidden_size, num_heads, num_kv_heads, head_dim, window (0 = none),
-    qkv_bias, out_bias, scale (optional), position (PartSpec or None)."""
+    qkv_bias, out_bias, scale (optional), position (PartSpec or None).
+
+    Further, all optional: value_dim (values of another size than keys), keep_first (with a window: the first
+    so many tokens of a sequence stay visible behind it, at their true positions), sinks (a learned logit per
+    query head, tensor ``sinks`` [num_heads], that joins the softmax's denominator without a key or a value),
+    value_mix ("source": this layer's values, as projected, are left for later layers of the step; "blend":
+    v <- (1 - a) v + a v_source with the scalar tensor ``value_mix`` = a, before v is cached; the tensor may be
+    stored for a source too, which ignores it).  A layer that uses any of these runs on the general attention
+    kernels (``csrc/attention_sink.cu``)."""
 
     graph_safe = True
     # portions of at least 16 rows go to the tensor-core attention in tiles of 128 query rows, the rest row by row
@@ -44,9 +53,19 @@ class Attention(Mixer):
         self.nq, self.nkv, self.hd = int(p["num_heads"]), int(p["num_kv_heads"]), int(p["head_dim"])
         if self.nq % self.nkv:
             raise ConfigError("num_heads must be a multiple of num_kv_heads")
-        if self.hd % 16 or self.hd > 256:
-            raise ConfigError(f"head_dim {self.hd} is not supported (multiples of 16 up to 256)")
+        self.vd = int(p.get("value_dim") or self.hd)
         self.window = int(p.get("window", 0) or 0)
+        self.keep_first = int(p.get("keep_first", 0) or 0) if self.window else 0
+        self.sinks = bool(p.get("sinks", False))
+        self.value_mix = p.get("value_mix")
+        if self.value_mix not in (None, "source", "blend"):
+            raise ConfigError(f"value_mix must be 'source' or 'blend', got {self.value_mix!r}")
+        self.general = bool(self.vd != self.hd or self.keep_first or self.sinks or self.value_mix)
+        if self.general:
+            if max(self.hd, self.vd) > 256 or min(self.hd, self.vd) < 1:
+                raise ConfigError(f"head sizes {self.hd} (keys) and {self.vd} (values) are not supported (1 to 256)")
+        elif self.hd % 16 or self.hd > 256:
+            raise ConfigError(f"head_dim {self.hd} is not supported (multiples of 16 up to 256)")
         self.qkv_bias = bool(p.get("qkv_bias", False))
         self.out_bias = bool(p.get("out_bias", False))
         self.scale = float(p["scale"]) if p.get("scale") is not None else 1.0 / math.sqrt(self.hd)
@@ -57,13 +76,17 @@ class Attention(Mixer):
             raise ConfigError("rotary_dim exceeds head_dim")
 
     def weights(self):
-        nq, nkv, hd, H = self.nq, self.nkv, self.hd, self.hidden
+        nq, nkv, hd, vd, H = self.nq, self.nkv, self.hd, self.vd, self.hidden
         w = {"q_proj.weight": mat(nq * hd, H), "k_proj.weight": mat(nkv * hd, H),
-             "v_proj.weight": mat(nkv * hd, H), "o_proj.weight": mat(H, nq * hd)}
+             "v_proj.weight": mat(nkv * vd, H), "o_proj.weight": mat(H, nq * vd)}
         if self.qkv_bias:
-            w.update({"q_proj.bias": vec(nq * hd), "k_proj.bias": vec(nkv * hd), "v_proj.bias": vec(nkv * hd)})
+            w.update({"q_proj.bias": vec(nq * hd), "k_proj.bias": vec(nkv * hd), "v_proj.bias": vec(nkv * vd)})
         if self.out_bias:
             w["o_proj.bias"] = vec(H)
+        if self.sinks:
+            w["sinks"] = vec(nq)
+        if "value_mix" in self.params:
+            w["value_mix"] = WeightSpec((), role="vector", optional=self.value_mix != "blend")
         return w
 
     def fused(self):
@@ -79,6 +102,9 @@ class Attention(Mixer):
                       if self.qkv_bias else None)
         self.w_o = t["o_proj.weight"]
         self.b_o = t.get("o_proj.bias")
+        self.sink = t.get("sinks")
+        # read once, when the tensors arrive: the kernels take the blend weight as a launch parameter
+        self.blend = float(t["value_mix"]) if self.value_mix == "blend" else 0.0
         if self.position is not None:
             self.cos, self.sin = self.position.tables()
         else:
@@ -88,10 +114,13 @@ class Attention(Mixer):
         return (self.w_qkv.dtype,)
 
     def cache_spec(self):
+        if self.general:
+            return KVSpec(self.nkv, self.hd, self.window, value_dim=None if self.vd == self.hd else self.vd,
+                          keep_first=self.keep_first)
         return KVSpec(self.nkv, self.hd, self.window)
 
     def step_needs(self):
-        return self.NEEDS
+        return None if self.general else self.NEEDS
 
     def plan_step(self, step, captured):
         """How the key ranges of a batch of decoded tokens are cut.  Requests of about the same length share one
@@ -100,6 +129,8 @@ class Attention(Mixer):
         needed as requests grow: four buckets per doubling of the context, at least 256 apart."""
         if step.n_tokens != len(step.entries):
             return None
+        if self.general:
+            return self._plan_general(step, captured)
         lens = [e.start_pos + 1 for e in step.entries]
         step.even_lengths = min(lens) * 4 >= max(lens) * 3
         if not captured:
@@ -109,9 +140,46 @@ class Attention(Mixer):
         step.max_kv_len = -(-kv // gran) * gran
         return (step.max_kv_len, step.even_lengths)
 
+    def _plan_general(self, step, captured):
+        """Decoded tokens on the general kernels: a captured step cuts its key ranges for a bucketed context
+        (buckets as above), which is part of the graph's key."""
+        if not captured:
+            return None
+        kv = max(step.max_kv_len, 1)
+        gran = max(256, 1 << max(kv.bit_length() - 3, 0))
+        step.max_kv_len = -(-kv // gran) * gran
+        return (step.max_kv_len,)
+
+    def _forward_general(self, xin, step, cache, writes_cache):
+        """Sizes and masks the fast kernels do not take: projection left as partial sums, one kernel that adds
+        them with the bias, rotates, blends the values and writes q and the cache rows, one attention kernel
+        with the window's kept first tokens and the sink, then the output projection as partial sums."""
+        if not writes_cache:
+            raise ModelError("attention: a layer on the general kernels owns its cache")
+        ops, nq, nkv, hd, vd = self.ops, self.nq, self.nkv, self.hd, self.vd
+        T, dev = xin.shape[0], xin.device
+        act = self.ctx.act_dtype if self.w_qkv.dtype == torch.bfloat16 else torch.float32
+        qkv = ops.gemm_partials(xin, self.w_qkv)
+        q = torch.empty((T, nq * hd), dtype=act, device=dev)
+        v_keep = v_from = None
+        if self.value_mix == "source":
+            v_keep = step.shared["attention.value_mix"] = torch.empty((T, nkv * vd), dtype=torch.float32, device=dev)
+        elif self.value_mix == "blend":
+            v_from = step.shared.get("attention.value_mix")
+            if v_from is None or tuple(v_from.shape) != (T, nkv * vd):
+                raise ModelError("attention: values are to be blended, but no earlier layer of the step left its own "
+                                 "(of the same size)")
+        ops.qkv_write(qkv, self.b_qkv, step.pos, step.slot, self.cos, self.sin, self.rot, self.rot_style, q, cache,
+                      nq, nkv, hd, vd, step.status, v_keep=v_keep, v_from=v_from, blend=self.blend)
+        attn = torch.empty((T, nq * vd), dtype=act, device=dev)
+        ops.sink_attention(q, cache, step, attn, nq, nkv, hd, vd, self.window, self.keep_first, self.sink, self.scale)
+        return Pending(partials=ops.gemm_partials(attn, self.w_o), bias=self.b_o)
+
     def forward(self, x, residual, step, cache, state, writes_cache=True):
         if cache is None:
             raise ModelError("attention needs a cache")
+        if self.general:
+            return self._forward_general(x[self.w_qkv.dtype], step, cache, writes_cache)
         ops, nq, nkv, hd = self.ops, self.nq, self.nkv, self.hd
         xin = x[self.w_qkv.dtype]
         T = xin.shape[0]

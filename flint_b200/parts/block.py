@@ -2,13 +2,15 @@
 
 ``prenorm``: h += mixer(norm1(h)); h += ffn(norm2(h)) -- the reference's decoder layer
 (crates/thuban_architectures/src/transformer/forward.rs:102-440) and Phi-MoE's.
-``parallel``: h += mixer(norm1(h)) + ffn(norm1(h)) with one shared norm (the feed-forward may be absent).
+``parallel``: h += mixer(norm1(h)) + ffn(norm1(h)) with one shared norm (the feed-forward may be absent);
+``parallel_two_norms``: h += mixer(norm1(h)) + ffn(norm2(h)), both of the same h.
 An arrangement only orders parts; it does not know what they are.
 """
 from __future__ import annotations
 
 import torch
 
+from ..errors import ConfigError
 from ..registry import BLOCKS
 from .base import Pending
 
@@ -100,3 +102,30 @@ class ParallelBlock(Block):
             return mixed
         fed = ffn.forward(x, residual, step, routed=routed) if routed is not None else ffn.forward(x, residual, step)
         return merge_pending(p["mixer"], residual, mixed, fed)
+
+
+@BLOCKS.register("parallel_two_norms")
+class ParallelTwoNormsBlock(Block):
+    """h += mixer(norm1(h)) + ffn(norm2(h)): both branches read the same rows, each through a norm of its own
+    (the feed-forward with its norm may be absent).  What the layer before left pending is applied by norm1's
+    kernel, so norm2 reads the finished rows; both branches' additions travel on to the next layer's norm."""
+    roles = ("norm1", "mixer")
+
+    def forward(self, residual, step, cache, state, writes_cache=True, carry=None):
+        p = self.parts
+        mixer, ffn = p["mixer"], p.get("ffn")
+        x, _ = run_norm(p["norm1"], residual, mixer.input_dtypes(), carry)
+        if ffn is None:
+            return mixer.forward(x, residual, step, cache, state, writes_cache)
+        if "norm2" not in p:
+            raise ConfigError("block 'parallel_two_norms': a feed-forward needs its norm (norm2)")
+        request = ffn.router_request(residual.shape[0]) if hasattr(ffn, "router_request") else None
+        routed_by_norm = request is not None and p["norm2"].supports_router
+        if routed_by_norm and step.record is not None and getattr(request, "logits", 0) is None:
+            request.logits = request.weight.new_empty((residual.shape[0], request.weight.shape[0]), dtype=torch.float32)
+        want = ffn.input_dtypes_when_routed() if routed_by_norm else ffn.input_dtypes()
+        # both norms read the rows before either branch may add to them
+        y, routed = run_norm(p["norm2"], residual, want, None, request if routed_by_norm else None)
+        mixed = mixer.forward(x, residual, step, cache, state, writes_cache)
+        fed = ffn.forward(y, residual, step, routed=routed) if routed is not None else ffn.forward(y, residual, step)
+        return merge_pending(mixer, residual, mixed, fed)

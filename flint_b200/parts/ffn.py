@@ -18,7 +18,9 @@ from .base import FeedForward, Pending, RouterRequest, mat, matmul_dtype
 
 @FEED_FORWARDS.register("gated_mlp")
 class GatedMLP(FeedForward):
-    """params: hidden_size, intermediate_size, act; tensors gate_proj/up_proj [I,H], down_proj [H,I]."""
+    """params: hidden_size, intermediate_size, act; tensors gate_proj/up_proj [I,H], down_proj [H,I].
+    act ``silu`` or ``gelu_pytorch_tanh``: act(gate) * up.  act ``swish_clamped`` with ``act_slope`` s and
+    ``act_limit`` c: g = min(gate, c), u = clamp(up, -c, c), g sigmoid(s g) (u + 1)."""
 
     graph_safe = True
 
@@ -26,6 +28,13 @@ class GatedMLP(FeedForward):
         super().__init__(params, ctx)
         self.hidden, self.inter = int(params["hidden_size"]), int(params["intermediate_size"])
         self.act = params.get("act", "silu")
+        self.act_params = None
+        if self.act == "swish_clamped":
+            self.act_params = (float(params["act_slope"]), float(params["act_limit"]))
+            if self.act_params[1] <= 0:
+                raise ConfigError(f"gated_mlp: act_limit must be positive, got {self.act_params[1]}")
+        elif self.act not in ("silu", "gelu_pytorch_tanh"):
+            raise ConfigError(f"gated_mlp: unknown activation {self.act!r}")
 
     def weights(self):
         return {"gate_proj.weight": mat(self.inter, self.hidden), "up_proj.weight": mat(self.inter, self.hidden),
@@ -46,7 +55,10 @@ class GatedMLP(FeedForward):
     def forward(self, x, residual, step):
         xin = x[self.w_gate_up.dtype]
         a = torch.empty((xin.shape[0], self.inter), dtype=self.w_gate_up.dtype, device=xin.device)
-        self.ops.gated_gemm(xin, self.w_gate_up, a, self.act)
+        if self.act_params is None:
+            self.ops.gated_gemm(xin, self.w_gate_up, a, self.act)
+        else:
+            self.ops.gated_gemm(xin, self.w_gate_up, a, self.act, act_params=self.act_params)
         self.ops.gemm(a, self.w_down, residual, accumulate=True)
 
 
@@ -202,3 +214,87 @@ class GroupedTopKMoE(FeedForward):
                 step.record.setdefault("router_logits", []).append(logits)
         # the weighted sum of the chosen experts' rows is added by the next norm's kernel
         return Pending(y=y, row_of=plan.row_of, gates=gates)
+
+
+@FEED_FORWARDS.register("sigmoid_topk_moe")
+class SigmoidTopKMoE(FeedForward):
+    """A mixture of small ungated experts, expert(x) = W_down act(W_up x), with a sigmoid router: scores
+    s = sigmoid(W_router x) in float32; the ``top`` experts with the largest scores are chosen (the lower index
+    among equals) and their scores are used as they are.  A score scales the expert's INPUT: the output is
+    sum_e expert_e(s_e x).  Since W_up is linear, act(W_up (s x)) = act(s (W_up x)): the score is applied to the
+    up product's float32 sums, before the activation.  An optional shared expert of the same form runs on every
+    token and is weighted by sigmoid(w_sg . x), one number a token; it rides along as one more row per token of
+    the experts' pending rows.  (No counterpart in the reference, whose feed-forward is dense:
+    crates/thuban_model/src/ops/mlp.rs:24-79.)
+
+    params: hidden_size, intermediate_size, num_experts, top, shared_intermediate_size (0: none), act ("gelu",
+    the erf form, or "gelu_pytorch_tanh", "silu").
+    tensors: router [E, H]; e{i}.up [I, H], e{i}.down [H, I]; shared.up [Is, H], shared.down [H, Is], shared.sg [1, H]."""
+
+    graph_safe = True
+
+    def __init__(self, params, ctx):
+        super().__init__(params, ctx)
+        p = params
+        self.hidden, self.inter = int(p["hidden_size"]), int(p["intermediate_size"])
+        self.E, self.top = int(p["num_experts"]), int(p["top"])
+        self.shared = int(p.get("shared_intermediate_size", 0) or 0)
+        self.act = p.get("act", "gelu")
+        if not 1 <= self.E <= 256:
+            raise ConfigError(f"num_experts {self.E} is not supported (1..256)")
+        if not 1 <= self.top <= min(self.E, 16):
+            raise ConfigError(f"{self.top} experts a token of {self.E} is not supported (1..16)")
+        if self.act not in ("gelu", "gelu_pytorch_tanh", "silu"):
+            raise ConfigError(f"sigmoid_topk_moe: unknown activation {self.act!r}")
+
+    def weights(self):
+        w = {"router": mat(self.E, self.hidden)}
+        for e in range(self.E):
+            w[f"e{e}.up"] = mat(self.inter, self.hidden)
+            w[f"e{e}.down"] = mat(self.hidden, self.inter)
+        if self.shared:
+            w.update({"shared.up": mat(self.shared, self.hidden), "shared.down": mat(self.hidden, self.shared),
+                      "shared.sg": mat(1, self.hidden)})
+        return w
+
+    def load(self, t):
+        # the shared expert's gate is one more row of the router's matrix: its logit comes with the experts'
+        self.w_router = torch.cat([t["router"], t["shared.sg"].to(t["router"].dtype)], 0).contiguous() if self.shared \
+            else t["router"]
+        dt = matmul_dtype(*(v for k, v in t.items() if k not in ("router", "shared.sg")))
+        self.w_up = torch.stack([t[f"e{e}.up"].to(dt) for e in range(self.E)], 0).contiguous()
+        self.w_down = torch.stack([t[f"e{e}.down"].to(dt) for e in range(self.E)], 0).contiguous()
+        if self.shared:
+            self.w_sup, self.w_sdown = t["shared.up"].to(dt), t["shared.down"].to(dt)
+
+    def input_dtypes(self):
+        return (torch.float32, self.w_up.dtype)       # the router reads the float32 rows
+
+    def forward(self, x, residual, step, routed=None):
+        ops = self.ops
+        xa = x[self.w_up.dtype]
+        T, dev, k, extra = xa.shape[0], xa.device, self.top, 1 if self.shared else 0
+        ids = torch.empty((T, k), dtype=torch.int32, device=dev)
+        scores = torch.empty((T, k), dtype=torch.float32, device=dev)
+        # what the pending rows are weighted by when they are added: 1 for the experts (their score went into
+        # their input), the sigmoid gate for the shared expert
+        weights = torch.empty((T, k + extra), dtype=torch.float32, device=dev)
+        logits = torch.empty((T, self.E + extra), dtype=torch.float32, device=dev) if step.record is not None else None
+        ops.router_sigmoid(x[torch.float32], self.w_router, self.E, k, ids, scores, weights, logits)
+        plan, xs = ops.moe_dispatch(ids, self.E, ops.moe_tile_rows(T, self.E, self.w_up.dtype, k), xa)
+        a = torch.empty((k * T, self.inter), dtype=self.w_up.dtype, device=dev)
+        ops.row_act(ops.gemm_partials(xs, self.w_up, plan=plan), a, self.act, row_of=plan.row_of, row_scale=scores)
+        y = torch.empty(((k + extra) * T, self.hidden), dtype=torch.float32, device=dev)
+        ops.grouped_gemm(a, self.w_down, y[:k * T], plan, plan_ready=True)
+        row_of = plan.row_of
+        if self.shared:
+            b = torch.empty((T, self.shared), dtype=self.w_up.dtype, device=dev)
+            ops.row_act(ops.gemm_partials(xa, self.w_sup), b, self.act)
+            ops.gemm(b, self.w_sdown, y[k * T:])
+            own = torch.arange(k * T, (k + 1) * T, dtype=torch.int32, device=dev)
+            row_of = torch.cat([row_of, own[:, None]], 1)
+        if step.record is not None:
+            step.record.setdefault("experts", []).append(ids)
+            step.record.setdefault("gates", []).append(scores)
+            step.record.setdefault("router_logits", []).append(logits)
+        return Pending(y=y, row_of=row_of, gates=weights)

@@ -1,7 +1,8 @@
 """Norm parts: LayerNorm (with or without bias) and RMSNorm.
 
 LayerNorm: y = (x - mean) * rsqrt(var + eps) * gamma + beta with var = mean((x-mean)^2);
-RMSNorm: y = x * rsqrt(mean(x^2) + eps) * gamma.  Statistics are float32.  The
+RMSNorm: y = x * rsqrt(mean(x^2) + eps) * gamma; with ``weight_offset`` c the stored scale w is an offset,
+gamma = c + w (formed once, in float32, when the tensors are loaded).  Statistics are float32.  The
 reference's norm shader has both as modes (crates/thuban_kernel/wgsl/norm.wgsl:66-83,
 112-121) and picks by config key (crates/thuban_architectures/src/phi.rs:55-63).
 """
@@ -22,16 +23,20 @@ class _RowNorm(Norm):
         self.width = int(params["width"])
         self.eps = float(params["eps"])
         self.has_bias = bool(params.get("bias", False))
+        # a scale stored as an offset: the row is multiplied by weight_offset + w (0: by w itself)
+        self.weight_offset = float(params.get("weight_offset", 0.0))
         self.gamma = self.beta = None
 
     def weights(self):
-        w = {"weight": vec(self.width, init="gamma")}
+        w = {"weight": vec(self.width, init="normal" if self.weight_offset else "gamma")}
         if self.has_bias:
             w["bias"] = vec(self.width)
         return w
 
     def load(self, tensors):
         self.gamma = tensors["weight"]
+        if self.weight_offset:
+            self.gamma = (self.gamma.to(torch.float32) + self.weight_offset).contiguous()
         self.beta = tensors.get("bias")
 
     supports_pending = True

@@ -17,6 +17,10 @@ from flint_b200.csrc.ops import MoePlan
 def _act(g, name):
     if name == "silu":
         return g / (1.0 + torch.exp(-g))
+    if name == "gelu":
+        return 0.5 * g * (1.0 + torch.erf(g / math.sqrt(2.0)))
+    if name == "none":
+        return g
     return 0.5 * g * (1.0 + torch.tanh(0.7978845608028654 * (g + 0.044715 * g ** 3)))
 
 
@@ -154,10 +158,16 @@ class RefOps:
         """This implementation keeps the gate rows before the up rows."""
         return torch.cat([w_gate, w_up], -2)
 
-    def gated_gemm(self, x, w13, out, act="silu", plan=None):
+    def gated_gemm(self, x, w13, out, act="silu", plan=None, act_params=None):
         """w13 = pair_gate_up(gate, up): [2N, K] or [E, 2N, K]."""
         xs = x.to(self.cd)
         n = w13.shape[-2] // 2
+        if act == "swish_clamped":
+            slope, limit = act_params
+            g = torch.clamp(xs @ w13[:n].to(self.cd).T, max=limit)
+            u = torch.clamp(xs @ w13[n:].to(self.cd).T, -limit, limit)
+            out.copy_((g * torch.sigmoid(slope * g) * (u + 1.0)).to(out.dtype))
+            return
         if plan is None:
             out.copy_((_act(xs @ w13[:n].to(self.cd).T, act) * (xs @ w13[n:].to(self.cd).T)).to(out.dtype))
             return
@@ -197,6 +207,125 @@ class RefOps:
 
     def moe_tile_rows(self, n_tokens, n_experts, weight_dtype, top=2):
         return 64
+
+    # ------------------------------------------------------------------ attention with kept first tokens and a sink
+    def qkv_write(self, qkv, bias, pos, slot, cos, sin, rot, style, q_out, cache, nq, nkv, hd, vd, status,
+                  v_keep=None, v_from=None, blend=0.0):
+        x = qkv.to(self.cd).sum(0) if qkv.dim() == 3 else qkv.to(self.cd)
+        if bias is not None:
+            x = x + bias.to(self.cd)
+        T = x.shape[0]
+        p = pos.long()
+        half = rot // 2
+
+        def rotate(h):
+            if rot == 0:
+                return h
+            c, s_ = cos[p].to(self.cd)[:, None, :], sin[p].to(self.cd)[:, None, :]
+            if style == "interleaved":
+                a, b = h[..., 0:rot:2], h[..., 1:rot:2]
+                both = torch.stack([a * c - b * s_, b * c + a * s_], -1).reshape(*h.shape[:-1], rot)
+            else:
+                a, b = h[..., :half], h[..., half:rot]
+                both = torch.cat([a * c - b * s_, b * c + a * s_], -1)
+            return torch.cat([both, h[..., rot:]], -1)
+        q = rotate(x[:, :nq * hd].view(T, nq, hd))
+        k = rotate(x[:, nq * hd:(nq + nkv) * hd].view(T, nkv, hd))
+        v = x[:, (nq + nkv) * hd:].view(T, nkv, vd)
+        if v_keep is not None:
+            v_keep.copy_(v.reshape(T, nkv * vd).to(v_keep.dtype))
+        if v_from is not None:
+            v = (1.0 - blend) * v + blend * v_from.to(self.cd).view(T, nkv, vd)
+        q_out.copy_(q.reshape(T, nq * hd).to(q_out.dtype))
+        P = cache.page_size
+        pages = cache.block_table[slot.long(), p // P].long()
+        assert (pages >= 0).all(), "write to a position without a page"
+        cache.k[pages, :, p % P, :] = k.to(cache.k.dtype)
+        cache.v[pages, :, p % P, :] = v.to(cache.v.dtype)
+
+    def sink_attention(self, q, cache, step, out, nq, nkv, hd, vd, window, keep_first, sinks, scale, splits=None):
+        T, P, G = q.shape[0], cache.page_size, nq // nkv
+        qq = q.to(self.cd).view(T, nq, hd)
+        res = torch.zeros(T, nq, vd, dtype=self.cd)
+        for t in range(T):
+            p = int(step.pos[t])
+            lo = max(0, p + 1 - window) if window else 0
+            js = torch.cat([torch.arange(0, min(keep_first, lo)), torch.arange(lo, p + 1)])
+            pages = cache.block_table[int(step.slot[t]), js // P].long()
+            assert (pages >= 0).all(), f"row {t}: key without a page"
+            k = cache.k[pages, :, js % P, :].to(self.cd)
+            v = cache.v[pages, :, js % P, :].to(self.cd)
+            for h in range(nq):
+                s = (k[:, h // G, :] @ qq[t, h]) * scale
+                if sinks is not None:
+                    s = torch.cat([s, sinks[h].to(self.cd).view(1)])
+                w = torch.softmax(s, 0)[:js.numel()]
+                res[t, h] = w @ v[:, h // G, :]
+        out.copy_(res.reshape(T, nq * vd).to(out.dtype))
+
+    # ------------------------------------------------------------------ matrix memory
+    def mlstm_scan(self, proj, b_gates, slot, seq_start, n_seq, state, out, H, D, V, cap):
+        x = proj.to(self.cd).sum(0) if proj.dim() == 3 else proj.to(self.cd)
+        T = x.shape[0]
+        o_q, o_k, o_v, o_g, o_i = 0, H * D, 2 * H * D, 2 * H * D + H * V, 2 * H * D + 2 * H * V
+        q = x[:, o_q:o_k].view(T, H, D) * D ** -0.5
+        k = x[:, o_k:o_v].view(T, H, D)
+        v = x[:, o_v:o_g].view(T, H, V)
+        zi = x[:, o_i:o_i + H] + b_gates[:H].to(self.cd)
+        zf = x[:, o_i + H:o_i + 2 * H] + b_gates[H:].to(self.cd)
+        gi = cap * torch.tanh(zi / cap)
+        gf = torch.nn.functional.logsigmoid(cap * torch.tanh(zf / cap))
+        starts = list(range(n_seq + 1)) if seq_start is None else seq_start.tolist()
+        per = D * V + D + 1
+        res = torch.zeros(T, H, V, dtype=self.cd)
+        for e in range(n_seq):
+            sl = int(slot[starts[e]])
+            st = state[sl].to(self.cd).clone()
+            for h in range(H):
+                S = st[h * per:h * per + D * V].view(V, D).T.clone()
+                n = st[h * per + D * V:h * per + D * V + D].clone()
+                m = st[h * per + D * V + D].clone()
+                for t in range(starts[e], starts[e + 1]):
+                    m_new = torch.maximum(gf[t, h] + m, gi[t, h])
+                    a, b = torch.exp(gf[t, h] + m - m_new), torch.exp(gi[t, h] - m_new)
+                    S = a * S + b * torch.outer(k[t, h], v[t, h])
+                    n = a * n + b * k[t, h]
+                    m = m_new
+                    res[t, h] = (S.T @ q[t, h]) / (torch.maximum(torch.abs(n @ q[t, h]), torch.exp(-m)) + 1e-6)
+                st[h * per:h * per + D * V] = S.T.reshape(-1)
+                st[h * per + D * V:h * per + D * V + D] = n
+                st[h * per + D * V + D] = m
+            state[sl] = st.to(state.dtype)
+        out.copy_(res.reshape(T, H * V).to(out.dtype))
+        return x[:, o_g:o_i].to(torch.float32)
+
+    def mlstm_finish(self, o, gate, norm_w, eps, out, H, V):
+        T = o.shape[0]
+        x = o.to(self.cd).view(T, H, V)
+        x = x / torch.sqrt((x * x).mean(-1, keepdim=True) + eps)
+        y = x.reshape(T, H * V) * norm_w.to(self.cd) * torch.sigmoid(gate.to(self.cd))
+        out.copy_(y.to(out.dtype))
+
+    # ------------------------------------------------------------------ sigmoid router, plain experts
+    def router_sigmoid(self, x, wr, E, top, expert_ids, scores, weights, logits_out=None):
+        z = x.to(self.cd) @ wr.to(self.cd).T
+        s = torch.sigmoid(z)
+        val, idx = torch.sort(s[:, :E], dim=-1, descending=True, stable=True)
+        expert_ids.copy_(idx[:, :top].to(torch.int32))
+        scores.copy_(val[:, :top].to(scores.dtype))
+        weights[:, :top] = 1.0
+        if wr.shape[0] > E:
+            weights[:, top:] = s[:, E:].to(weights.dtype)
+        if logits_out is not None:
+            logits_out.copy_(z.to(logits_out.dtype))
+
+    def row_act(self, partials, out, act, row_of=None, row_scale=None):
+        x = partials.to(self.cd).sum(0) if partials.dim() == 3 else partials.to(self.cd)
+        if row_of is not None:
+            scale = torch.ones(x.shape[0], dtype=self.cd)
+            scale[row_of.reshape(-1).long()] = row_scale.reshape(-1).to(self.cd)
+            x = x * scale[:, None]
+        out.copy_(_act(x, act).to(out.dtype))
 
     # ------------------------------------------------------------------ attention over a cached latent
     def head_products(self, x, w, out):
