@@ -7,9 +7,10 @@
 // Three kernels.  flint_mlstm_prepare adds up the partial sums of the input projection [q | k | v | g | z_i | z_f]
 // and turns them into what the recurrence reads: q times D^(-1/2), i = cap tanh((z_i + b_i) / cap),
 // f = logsigmoid(cap tanh((z_f + b_f) / cap)); it is parallel over tokens.  flint_mlstm_scan walks the tokens of
-// every request in order: a warp owns CW columns of one head's S (lane l holds rows l, l + 32, ... of each) and a
-// copy of n and m, so no warp waits for another; the next token's operands are fetched while the current one is
-// worked.  The state is read from and written back to the request's row of the state slab
+// every request in order, in two kernels: one warp per (request, head) carries m and n and leaves every token's
+// decay, intake and denominator; then a warp per CW columns of one head's S (lane l holds rows l, l + 32, ... of
+// each) carries those columns, so no warp waits for another or touches another's part of the state; the next
+// token's operands are fetched while the current one is worked.  The state is read from and written back to the request's row of the state slab
 // (per head: S transposed [V, D], then n [D], then m), so a prompt cut anywhere gives the same numbers.
 // flint_mlstm_finish divides each head's o by its root mean square and applies the scale and the output gate.
 //
@@ -49,11 +50,80 @@ __global__ void mlstm_prepare_kernel(const float* __restrict__ partials, int S, 
   x[i] = v;
 }
 
+// The part of the recurrence that all columns of a head share: m, n and the denominator.  A warp per (request,
+// head) walks the request's tokens and leaves, per token, the decay e^(f + m - m'), the intake e^(i - m') and the
+// denominator max(|n' . q|, e^(-m')) + 1e-6 in coef [T, H, 4]; it alone reads and writes n and m of the state.
+template <int ND>
+__global__ void __launch_bounds__(SCAN_WARPS * 32)
+mlstm_gate_scan_kernel(const float* __restrict__ x, int N, const int* __restrict__ slot, const int* __restrict__ seq_start,
+                       int n_seq, float* __restrict__ state, long long state_stride, float* __restrict__ coef, int H,
+                       int D, int V) {
+  pdl_launch();
+  pdl_wait();
+  const int lane = threadIdx.x & 31;
+  const long long item = (long long)blockIdx.x * SCAN_WARPS + (threadIdx.x >> 5);
+  if (item >= (long long)n_seq * H) return;
+  const int h = (int)(item % H), e = (int)(item / H);
+  const int t0 = seq_start ? seq_start[e] : e, t1 = seq_start ? seq_start[e + 1] : e + 1;
+  if (t1 <= t0) return;
+  float* st = state + (size_t)slot[t0] * state_stride + (size_t)h * ((size_t)D * V + D + 1) + (size_t)D * V;
+  float nv[ND];
+#pragma unroll
+  for (int i = 0; i < ND; ++i) nv[i] = lane + 32 * i < D ? st[lane + 32 * i] : 0.f;
+  float m = st[D];
+  const int oq = h * D, ok = H * D + h * D, oi = 2 * H * D + 2 * H * V + h;
+  float q[ND], k[ND], gi, gf;
+  auto fetch = [&](int t, float* qq, float* kk, float& ii, float& ff) {
+    const float* row = x + (size_t)t * N;
+#pragma unroll
+    for (int i = 0; i < ND; ++i) {
+      const int d = lane + 32 * i;
+      qq[i] = d < D ? row[oq + d] : 0.f;
+      kk[i] = d < D ? row[ok + d] : 0.f;
+    }
+    ii = row[oi];
+    ff = row[oi + H];
+  };
+  fetch(t0, q, k, gi, gf);
+  for (int t = t0; t < t1; ++t) {
+    float qn[ND], kn[ND], gin = 0.f, gfn = 0.f;
+    if (t + 1 < t1) fetch(t + 1, qn, kn, gin, gfn);
+    const float m_new = fmaxf(gf + m, gi);
+    const float a = expf(gf + m - m_new), b = expf(gi - m_new);
+    float nq = 0.f;
+#pragma unroll
+    for (int i = 0; i < ND; ++i) {
+      nv[i] = fmaf(a, nv[i], b * k[i]);
+      nq = fmaf(nv[i], q[i], nq);
+    }
+    nq = warp_sum(nq);
+    if (lane == 0) {
+      float* c = coef + ((size_t)t * H + h) * 4;
+      c[0] = a;
+      c[1] = b;
+      c[2] = fmaxf(fabsf(nq), expf(-m_new)) + 1e-6f;
+    }
+    m = m_new;
+    if (t + 1 < t1) {
+#pragma unroll
+      for (int i = 0; i < ND; ++i) { q[i] = qn[i]; k[i] = kn[i]; }
+      gi = gin;
+      gf = gfn;
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < ND; ++i)
+    if (lane + 32 * i < D) st[lane + 32 * i] = nv[i];
+  if (lane == 0) st[D] = m;
+}
+
+// The matrix memory itself: a warp owns CW columns of one head's S (no other warp touches them), lane l rows l,
+// l + 32, ...; per token S' = a S + (b k) v^T and o = S'^T q / denominator, with a, b and the denominator from coef.
 template <int ND>
 __global__ void __launch_bounds__(SCAN_WARPS * 32)
 mlstm_scan_kernel(const float* __restrict__ x, int N, const int* __restrict__ slot, const int* __restrict__ seq_start,
-                  int n_seq, float* __restrict__ state, long long state_stride, float* __restrict__ out, int H, int D,
-                  int V, int col_groups) {
+                  int n_seq, float* __restrict__ state, long long state_stride, const float* __restrict__ coef,
+                  float* __restrict__ out, int H, int D, int V, int col_groups) {
   pdl_launch();
   pdl_wait();
   const int lane = threadIdx.x & 31;
@@ -64,18 +134,16 @@ mlstm_scan_kernel(const float* __restrict__ x, int N, const int* __restrict__ sl
   if (t1 <= t0) return;
   float* st = state + (size_t)slot[t0] * state_stride + (size_t)h * ((size_t)D * V + D + 1);
   const int c0 = cg * CW;
-  float Sm[CW][ND], nv[ND];
+  float Sm[CW][ND];
 #pragma unroll
   for (int i = 0; i < ND; ++i) {
     const int d = lane + 32 * i;
-    nv[i] = d < D ? st[(size_t)D * V + d] : 0.f;
 #pragma unroll
     for (int c = 0; c < CW; ++c) Sm[c][i] = (d < D && c0 + c < V) ? st[(size_t)(c0 + c) * D + d] : 0.f;
   }
-  float m = st[(size_t)D * V + D];
-  const int oq = h * D, ok = H * D + h * D, ov = 2 * H * D + h * V + c0, oi = 2 * H * D + 2 * H * V + h;
-  float q[ND], k[ND], v[CW], gi, gf;
-  auto fetch = [&](int t, float* qq, float* kk, float* vv, float& ii, float& ff) {
+  const int oq = h * D, ok = H * D + h * D, ov = 2 * H * D + h * V + c0;
+  float q[ND], k[ND], v[CW], a, b, den;
+  auto fetch = [&](int t, float* qq, float* kk, float* vv, float& aa, float& bb, float& dd) {
     const float* row = x + (size_t)t * N;
 #pragma unroll
     for (int i = 0; i < ND; ++i) {
@@ -85,58 +153,52 @@ mlstm_scan_kernel(const float* __restrict__ x, int N, const int* __restrict__ sl
     }
 #pragma unroll
     for (int c = 0; c < CW; ++c) vv[c] = c0 + c < V ? row[ov + c] : 0.f;
-    ii = row[oi];
-    ff = row[oi + H];
+    const float* cf = coef + ((size_t)t * H + h) * 4;
+    aa = cf[0];
+    bb = cf[1];
+    dd = cf[2];
   };
-  fetch(t0, q, k, v, gi, gf);
+  fetch(t0, q, k, v, a, b, den);
   for (int t = t0; t < t1; ++t) {
-    float qn[ND], kn[ND], vn[CW], gin = 0.f, gfn = 0.f;
-    if (t + 1 < t1) fetch(t + 1, qn, kn, vn, gin, gfn);
-    const float m_new = fmaxf(gf + m, gi);
-    const float a = expf(gf + m - m_new), b = expf(gi - m_new);
-    float nq = 0.f, acc[CW];
+    float qn[ND], kn[ND], vn[CW], an = 0.f, bn = 0.f, dn = 1.f;
+    if (t + 1 < t1) fetch(t + 1, qn, kn, vn, an, bn, dn);
+    float acc[CW];
 #pragma unroll
     for (int c = 0; c < CW; ++c) acc[c] = 0.f;
 #pragma unroll
     for (int i = 0; i < ND; ++i) {
       const float bk = b * k[i];
-      nv[i] = fmaf(a, nv[i], bk);
-      nq = fmaf(nv[i], q[i], nq);
 #pragma unroll
       for (int c = 0; c < CW; ++c) {
         Sm[c][i] = fmaf(a, Sm[c][i], bk * v[c]);
         acc[c] = fmaf(Sm[c][i], q[i], acc[c]);
       }
     }
-    nq = warp_sum(nq);
 #pragma unroll
     for (int c = 0; c < CW; ++c) acc[c] = warp_sum(acc[c]);
-    const float den = fmaxf(fabsf(nq), expf(-m_new)) + 1e-6f;
     float mine = acc[0];
 #pragma unroll
     for (int c = 1; c < CW; ++c) mine = lane == c ? acc[c] : mine;
     if (lane < CW && c0 + lane < V) out[((size_t)t * H + h) * V + c0 + lane] = mine / den;
-    m = m_new;
     if (t + 1 < t1) {
 #pragma unroll
       for (int i = 0; i < ND; ++i) { q[i] = qn[i]; k[i] = kn[i]; }
 #pragma unroll
       for (int c = 0; c < CW; ++c) v[c] = vn[c];
-      gi = gin;
-      gf = gfn;
+      a = an;
+      b = bn;
+      den = dn;
     }
   }
 #pragma unroll
   for (int i = 0; i < ND; ++i) {
     const int d = lane + 32 * i;
     if (d < D) {
-      if (cg == 0) st[(size_t)D * V + d] = nv[i];
 #pragma unroll
       for (int c = 0; c < CW; ++c)
         if (c0 + c < V) st[(size_t)(c0 + c) * D + d] = Sm[c][i];
     }
   }
-  if (cg == 0 && lane == 0) st[(size_t)D * V + D] = m;
 }
 
 // out[t, h, c] = o[t, h, c] / sqrt(mean_c o[t, h, :]^2 + eps) * w[h V + c] * sigmoid(gate[t, h V + c]); a warp per (t, h)
@@ -178,19 +240,26 @@ extern "C" int flint_mlstm_prepare(const float* partials, int S, long long strid
 }
 
 // x [T, N] as flint_mlstm_prepare leaves it; the rows of request e are seq_start[e] .. seq_start[e + 1] - 1 (NULL:
-// row e alone); state [slots, state_stride] float32; out [T, H V] float32.
+// row e alone); state [slots, state_stride] float32; coef [T, H, 4] float32 scratch; out [T, H V] float32.
 extern "C" int flint_mlstm_scan(const float* x, const int* slot, const int* seq_start, int n_seq, float* state,
-                                long long state_stride, float* out, int T, int H, int D, int V, cudaStream_t stream) {
+                                long long state_stride, float* coef, float* out, int T, int H, int D, int V,
+                                cudaStream_t stream) {
   if (T <= 0 || n_seq <= 0) return 0;
   if (H < 1 || D < 1 || V < 1 || D > 256) return fail("mlstm_scan: %d heads of %d x %d are not supported (dims up to 256)", H, D, V);
   if (state_stride < (long long)H * ((long long)D * V + D + 1)) return fail("mlstm_scan: the state rows are too short");
   if (!seq_start && n_seq != T) return fail("mlstm_scan: without a list of starts every request brings one row");
   const int N = 2 * H * D + 2 * H * V + 2 * H;
   const int col_groups = (V + CW - 1) / CW;
-  const long long items = (long long)n_seq * H * col_groups;
+  const long long gate_items = (long long)n_seq * H, items = gate_items * col_groups;
+  const dim3 gate_grid((unsigned)((gate_items + SCAN_WARPS - 1) / SCAN_WARPS));
   const dim3 grid((unsigned)((items + SCAN_WARPS - 1) / SCAN_WARPS)), block(SCAN_WARPS * 32);
-#define SCAN(ND) launch_pdl(mlstm_scan_kernel<ND>, grid, block, 0, stream, x, N, slot, seq_start, n_seq, state, \
-                            state_stride, out, H, D, V, col_groups)
+#define SCAN(ND)                                                                                                     \
+  do {                                                                                                               \
+    launch_pdl(mlstm_gate_scan_kernel<ND>, gate_grid, block, 0, stream, x, N, slot, seq_start, n_seq, state,         \
+               state_stride, coef, H, D, V);                                                                         \
+    launch_pdl(mlstm_scan_kernel<ND>, grid, block, 0, stream, x, N, slot, seq_start, n_seq, state, state_stride,     \
+               (const float*)coef, out, H, D, V, col_groups);                                                        \
+  } while (0)
   if (D <= 32) SCAN(1);
   else if (D <= 64) SCAN(2);
   else if (D <= 128) SCAN(4);

@@ -839,8 +839,9 @@ class CudaOps:
         x = torch.empty((T, N), dtype=torch.float32, device=proj.device)
         self._run("mlstm", "flint_mlstm_prepare", _ptr(proj), c_int(S), c_longlong(proj.stride(0)), _ptr(b_gates), _ptr(x),
                   c_int(T), c_int(H), c_int(D), c_int(V), c_float(cap))
+        coef = torch.empty((T, H, 4), dtype=torch.float32, device=proj.device)
         self._run("mlstm", "flint_mlstm_scan", _ptr(x), _ptr(slot), _ptr(seq_start), c_int(n_seq), _ptr(state),
-                  c_longlong(state.stride(0)), _ptr(out), c_int(T), c_int(H), c_int(D), c_int(V))
+                  c_longlong(state.stride(0)), _ptr(coef), _ptr(out), c_int(T), c_int(H), c_int(D), c_int(V))
         g0 = 2 * H * D + H * V
         return x[:, g0:g0 + H * V]
 

@@ -69,7 +69,7 @@ class MatrixLSTM(Mixer):
         batch).  A batch of single decoded tokens needs no list: row r is request r."""
         if step.n_tokens != len(step.entries):
             starts = torch.tensor(list(step.entry_start) + [step.n_tokens], dtype=torch.int32)
-            step.plans["mlstm.seq_start"] = starts.to(step.pos.device, non_blocking=True)
+            step.plans["mlstm.seq_start"] = starts.to(step.pos.device)
         return None
 
     def forward(self, x, residual, step, cache, state, writes_cache=True):
