@@ -43,10 +43,12 @@ class GepadraArchitecture:
                 if m.v_mix:
                     role = "source" if first_mix is None else "blend"
                     first_mix = i if first_mix is None else first_mix
-                mixer = PartSpec("attention", {
-                    "hidden_size": cfg.width, "num_heads": m.heads, "num_kv_heads": m.kv_heads, "head_dim": m.dim,
-                    "value_dim": m.vdim, "window": m.window, "keep_first": m.keep_first, "qkv_bias": True,
-                    "scale": m.scale, "sinks": True, "value_mix": role, "position": position})
+                params = {"hidden_size": cfg.width, "num_heads": m.heads, "num_kv_heads": m.kv_heads, "head_dim": m.dim,
+                          "value_dim": m.vdim, "window": m.window, "keep_first": m.keep_first, "qkv_bias": True,
+                          "scale": m.scale, "sinks": True, "position": position}
+                if role is not None:
+                    params["value_mix"] = role      # such a layer stores a blend weight, also the first, which ignores it
+                mixer = PartSpec("attention", params)
                 for ours, theirs in (("q_proj.weight", "q"), ("k_proj.weight", "k"), ("v_proj.weight", "v"),
                                      ("o_proj.weight", "o"), ("q_proj.bias", "q.b"), ("k_proj.bias", "k.b"),
                                      ("v_proj.bias", "v.b"), ("sinks", "sink"), ("value_mix", "vmix")):
