@@ -449,8 +449,39 @@ PULEDRA_SIZES = {
 }
 
 
+def gepadra_config(width, heads, kv_heads, dim, vdim, window, keep, rot, m_heads, m_dim, m_vdim, ff, experts, top, shared,
+                   dense_ff, layers, vocab, every=3):
+    """A Gepadra configuration of ``layers`` layers: every ``every``-th an attention layer (sliding window with kept
+    first tokens, sinks, blended values), the others mLSTM layers; the first layer's feed-forward is the clamped
+    gated unit, the others' a mixture of ungated experts with a shared one."""
+    out = []
+    for i in range(layers):
+        if i % every == every - 1:
+            kind, m = "attention", {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "scale": dim ** -0.5,
+                                    "mask": {"size": window, "keep_first": keep}, "rot": {"dims": rot, "base": 1e6}, "v_mix": True}
+        else:
+            kind, m = "mlstm", {"heads": m_heads, "dim": m_dim, "vdim": m_vdim, "gate_cap": 15.0}
+        mlp = {"kind": "dense", "ff": dense_ff, "limit": 7.0} if i == 0 else \
+            {"kind": "moe", "expert": {"ff": ff}, "router": {"experts": experts, "top": top}, "shared": {"ff": shared}}
+        out.append({"type": kind, "mixer": m, "mlp": mlp})
+    return {"architecture": "Gepadra", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "layers": out}
+
+
+# layer sizes that resemble real models of this kind, beside the Phi-MoE layer of equal width, head count and head size
+GEPADRA_SIZES = {
+    "2048x16": dict(width=2048, heads=16, kv_heads=4, dim=128, vdim=128, window=1024, keep=4, rot=64, m_heads=4, m_dim=256,
+                    m_vdim=512, ff=2112, experts=16, top=2, shared=2112, dense_ff=5632,
+                    phi=dict(hidden_size=2048, num_attention_heads=16, num_key_value_heads=4, head_dim=128,
+                             intermediate_size=1408, num_local_experts=16)),
+    "4096x32": dict(width=4096, heads=32, kv_heads=8, dim=128, vdim=128, window=1024, keep=4, rot=64, m_heads=8, m_dim=256,
+                    m_vdim=512, ff=1440, experts=16, top=2, shared=1440, dense_ff=8192,
+                    phi=dict(hidden_size=4096, num_attention_heads=32, num_key_value_heads=8, head_dim=128,
+                             intermediate_size=960, num_local_experts=16)),
+}
+
+
 def run_design_pair(args, pk, rng):
-    """Prefill and decode of Puledra at layer sizes that resemble real models, beside Phi-MoE at equal width, heads
+    """Prefill and decode of Puledra or Gepadra at layer sizes that resemble real models, beside Phi-MoE at equal width, heads
     and active expert parameters: tokens/s, and for the attention kernels of both the time a layer and the
     fraction of the measured peak (decode: cache bytes over the copy bandwidth; prefill: flops over the sustained
     library product rate)."""
@@ -458,14 +489,16 @@ def run_design_pair(args, pk, rng):
     layers = args.layers or 8
     vocab = args.vocab or 32064
     batch, ctx = args.batch, args.prompt_tokens
-    out = {"design": "Puledra", "beside": "PhimoeForCausalLM", "layers": layers, "batch": batch, "prompt_tokens": ctx,
+    gep = args.design == "gepadra"
+    out = {"design": "Gepadra" if gep else "Puledra", "beside": "PhimoeForCausalLM", "layers": layers, "batch": batch, "prompt_tokens": ctx,
            "dtype": "bf16", "data": "synthetic: seeded random weights, uniform-random token ids",
            "peaks": {k: pk[k] for k in ("hbm_gbs", "bf16_tflops_sustained", "source")}, "sizes": {}}
-    for name, sz in PULEDRA_SIZES.items():
+    for name, sz in (GEPADRA_SIZES if gep else PULEDRA_SIZES).items():
         if args.design_sizes and name not in args.design_sizes:
             continue
         phi = sz["phi"]
-        cfgs = {"puledra": puledra_config(**{k: v for k, v in sz.items() if k != "phi"}, layers=layers, vocab=vocab),
+        make = gepadra_config if gep else puledra_config
+        cfgs = {args.design: make(**{k: v for k, v in sz.items() if k != "phi"}, layers=layers, vocab=vocab),
                 "phimoe": mini_config(layers, None, {**phi, "vocab_size": vocab})}
         row = {}
         for which, cfg in cfgs.items():
@@ -475,7 +508,18 @@ def run_design_pair(args, pk, rng):
             dec = run_decode(model, cfg, batch, ctx, args.steps, max(args.warmup, 3), rng, count_experts=False)
             pre_t, dec_t, _ = profile_tables(model, cfg, batch, ctx, rng)
             kv = ctx + 2
-            if which == "puledra":
+            state_bytes = 0
+            if which == "gepadra":
+                att = next(l.parts["mixer"] for l in model.layers if hasattr(l.parts["mixer"], "keep_first"))
+                rec = next(l.parts["mixer"] for l in model.layers if hasattr(l.parts["mixer"], "cap"))
+                n_att = sum(1 for l in model.layers if l.parts["mixer"] is not None and hasattr(l.parts["mixer"], "keep_first"))
+                seen = lambda k: min(k, att.window + att.keep_first) if att.window else k
+                att_bytes = batch * seen(kv) * att.nkv * (att.hd + att.vd) * 2
+                att_flops = sum(2 * att.nq * (att.hd + att.vd) * seen(k) for k in range(1, ctx + 1))
+                state_bytes = batch * rec.H * (rec.D * rec.V + rec.D + 1) * 4 * 2       # read and written every token
+                names = ("flint_sink_attention", "flint_qkv_write", "flint_mlstm", "flint_router_sigmoid", "flint_row_act",
+                         "flint_gated_act", "flint_row_norm")
+            elif which == "puledra":
                 m = model.layers[0].parts["mixer"]
                 att_bytes = batch * kv * m.row_w * 2
                 att_flops = sum(2 * m.H * (m.Dk + m.C) * k for k in range(1, ctx + 1))
@@ -490,8 +534,18 @@ def run_design_pair(args, pk, rng):
                 for kname, (n, ms) in sorted(table.items()):
                     if not kname.startswith(names):
                         continue
-                    e = {"launches": n, "us_per_layer": round(ms * 1000.0 / layers, 2)}
-                    if "attention" in kname and "prepare" not in kname:
+                    per = layers
+                    if which == "gepadra":       # a kernel runs in the layers of its kind only
+                        per = n_att if ("attention" in kname or "qkv_write" in kname) else (layers - n_att if "mlstm" in kname else layers)
+                    e = {"launches": n, "us_per_layer": round(ms * 1000.0 / per, 2)}
+                    if kname.startswith("flint_mlstm_scan") and kind == "decode":
+                        e["frac_of_copy_bandwidth"] = round(state_bytes / (ms / per * 1e-3) / 1e9 / pk["hbm_gbs"], 4)
+                    elif which == "gepadra" and kname.startswith("flint_sink_attention"):
+                        if kind == "decode":
+                            e["frac_of_copy_bandwidth"] = round(att_bytes / (ms / per * 1e-3) / 1e9 / pk["hbm_gbs"], 4)
+                        else:
+                            e["frac_of_sustained_product_rate"] = round(att_flops / (ms / per * 1e-3) / (pk["bf16_tflops_sustained"] * 1e12), 4)
+                    elif which != "gepadra" and "attention" in kname and "prepare" not in kname:
                         if kind == "decode":
                             e["frac_of_copy_bandwidth"] = round(att_bytes / (ms / layers * 1e-3) / 1e9 / pk["hbm_gbs"], 4)
                         else:
@@ -746,7 +800,7 @@ def main():
     ap.add_argument("--sweep", action="store_true",
                     help="instead of the default run: decode at batch 1 and 8 with contexts of 16,384 and 65,536 tokens, "
                          "batch 1 with 131,008, and batch 128 and 256 with 2,048, each with its roofline fraction")
-    ap.add_argument("--design", choices=["puledra"], default=None,
+    ap.add_argument("--design", choices=["puledra", "gepadra"], default=None,
                     help="prefill and decode of this design at layer sizes that resemble real models, beside Phi-MoE at "
                          "equal width, heads and active expert parameters, with the attention kernels' shares of the peaks")
     ap.add_argument("--design-sizes", nargs="+", default=None, help="which of the design's size points to run")

@@ -9,8 +9,8 @@
 // f = logsigmoid(cap tanh((z_f + b_f) / cap)); it is parallel over tokens.  flint_mlstm_scan walks the tokens of
 // every request in order, in two kernels: one warp per (request, head) carries m and n and leaves every token's
 // decay, intake and denominator; then a warp per CW columns of one head's S (lane l holds rows l, l + 32, ... of
-// each) carries those columns, so no warp waits for another or touches another's part of the state; the next
-// token's operands are fetched while the current one is worked.  The state is read from and written back to the request's row of the state slab
+// each) carries those columns, so no warp touches another's part of the state; a block stages the operands of 16
+// tokens at a time in shared memory, so the walk does not wait for global memory at every token.  The state is read from and written back to the request's row of the state slab
 // (per head: S transposed [V, D], then n [D], then m), so a prompt cut anywhere gives the same numbers.
 // flint_mlstm_finish divides each head's o by its root mean square and applies the scale and the output gate.
 //
@@ -26,6 +26,33 @@ namespace {
 
 constexpr int CW = 4;          // columns of S per warp
 constexpr int SCAN_WARPS = 4;  // warps per block of the scan
+constexpr int TCH = 16;        // tokens staged in shared memory at a time
+
+// Both scans walk a request's tokens one after the other, and what they read of a token does not depend on the
+// token before.  A block therefore brings the operands of TCH tokens into shared memory with all its threads
+// (q and k of the head, and whatever `more` adds), and the recurrence then runs on those without waiting for
+// global memory at every token.
+template <typename More>
+__device__ __forceinline__ void stage_tokens(const float* __restrict__ x, int N, int t_first, int n, int oq, int ok, int D,
+                                             float* q_s, float* k_s, More more) {
+  // a thread takes dims d, d + blockDim.x, ... of every staged token; the loads of all TCH tokens are in flight
+  // together (one after the other they would each cost a trip to L2)
+  for (int d = threadIdx.x; d < D; d += blockDim.x) {
+    float tq[TCH], tk[TCH];
+    const float* col = x + (size_t)t_first * N + d;
+#pragma unroll
+    for (int j = 0; j < TCH; ++j) {
+      tq[j] = j < n ? col[(size_t)j * N + oq] : 0.f;
+      tk[j] = j < n ? col[(size_t)j * N + ok] : 0.f;
+    }
+#pragma unroll
+    for (int j = 0; j < TCH; ++j) {
+      q_s[j * D + d] = tq[j];
+      k_s[j * D + d] = tk[j];
+    }
+  }
+  more();
+}
 
 __device__ __forceinline__ float log_sigmoid(float z) { return fminf(z, 0.f) - log1pf(expf(-fabsf(z))); }
 
@@ -50,90 +77,92 @@ __global__ void mlstm_prepare_kernel(const float* __restrict__ partials, int S, 
   x[i] = v;
 }
 
-// The part of the recurrence that all columns of a head share: m, n and the denominator.  A warp per (request,
-// head) walks the request's tokens and leaves, per token, the decay e^(f + m - m'), the intake e^(i - m') and the
-// denominator max(|n' . q|, e^(-m')) + 1e-6 in coef [T, H, 4]; it alone reads and writes n and m of the state.
+// The part of the recurrence that all columns of a head share: m, n and the denominator.  One block per (request,
+// head); its first warp walks the request's tokens and leaves, per token, the decay e^(f + m - m'), the intake
+// e^(i - m') and the denominator max(|n' . q|, e^(-m')) + 1e-6 in coef [T, H, 4]; it alone reads and writes n and
+// m of the state.
 template <int ND>
 __global__ void __launch_bounds__(SCAN_WARPS * 32)
 mlstm_gate_scan_kernel(const float* __restrict__ x, int N, const int* __restrict__ slot, const int* __restrict__ seq_start,
                        int n_seq, float* __restrict__ state, long long state_stride, float* __restrict__ coef, int H,
                        int D, int V) {
+  extern __shared__ float sm[];
+  float* q_s = sm;                       // [TCH][D]
+  float* k_s = q_s + TCH * D;            // [TCH][D]
+  float* g_s = k_s + TCH * D;            // [TCH][2]: log input gate, log forget gate
   pdl_launch();
   pdl_wait();
-  const int lane = threadIdx.x & 31;
-  const long long item = (long long)blockIdx.x * SCAN_WARPS + (threadIdx.x >> 5);
-  if (item >= (long long)n_seq * H) return;
-  const int h = (int)(item % H), e = (int)(item / H);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int h = blockIdx.x % H, e = blockIdx.x / H;
   const int t0 = seq_start ? seq_start[e] : e, t1 = seq_start ? seq_start[e + 1] : e + 1;
   if (t1 <= t0) return;
   float* st = state + (size_t)slot[t0] * state_stride + (size_t)h * ((size_t)D * V + D + 1) + (size_t)D * V;
   float nv[ND];
 #pragma unroll
-  for (int i = 0; i < ND; ++i) nv[i] = lane + 32 * i < D ? st[lane + 32 * i] : 0.f;
+  for (int i = 0; i < ND; ++i) nv[i] = (warp == 0 && lane + 32 * i < D) ? st[lane + 32 * i] : 0.f;
   float m = st[D];
   const int oq = h * D, ok = H * D + h * D, oi = 2 * H * D + 2 * H * V + h;
-  float q[ND], k[ND], gi, gf;
-  auto fetch = [&](int t, float* qq, float* kk, float& ii, float& ff) {
-    const float* row = x + (size_t)t * N;
+  for (int tc = t0; tc < t1; tc += TCH) {
+    const int n = min(TCH, t1 - tc);
+    stage_tokens(x, N, tc, n, oq, ok, D, q_s, k_s, [&] {
+      for (int j = threadIdx.x; j < 2 * n; j += blockDim.x) g_s[j] = x[(size_t)(tc + (j >> 1)) * N + oi + (j & 1) * H];
+    });
+    __syncthreads();
+    if (warp == 0) {
+      for (int j = 0; j < n; ++j) {
+        const float gi = g_s[2 * j], gf = g_s[2 * j + 1];
+        const float m_new = fmaxf(gf + m, gi);
+        const float a = expf(gf + m - m_new), b = expf(gi - m_new);
+        float nq = 0.f;
 #pragma unroll
-    for (int i = 0; i < ND; ++i) {
-      const int d = lane + 32 * i;
-      qq[i] = d < D ? row[oq + d] : 0.f;
-      kk[i] = d < D ? row[ok + d] : 0.f;
+        for (int i = 0; i < ND; ++i) {
+          const int d = lane + 32 * i;
+          if (d < D) {
+            nv[i] = fmaf(a, nv[i], b * k_s[j * D + d]);
+            nq = fmaf(nv[i], q_s[j * D + d], nq);
+          }
+        }
+        nq = warp_sum(nq);
+        if (lane == 0) {
+          float* c = coef + ((size_t)(tc + j) * H + h) * 4;
+          c[0] = a;
+          c[1] = b;
+          c[2] = fmaxf(fabsf(nq), expf(-m_new)) + 1e-6f;
+        }
+        m = m_new;
+      }
     }
-    ii = row[oi];
-    ff = row[oi + H];
-  };
-  fetch(t0, q, k, gi, gf);
-  for (int t = t0; t < t1; ++t) {
-    float qn[ND], kn[ND], gin = 0.f, gfn = 0.f;
-    if (t + 1 < t1) fetch(t + 1, qn, kn, gin, gfn);
-    const float m_new = fmaxf(gf + m, gi);
-    const float a = expf(gf + m - m_new), b = expf(gi - m_new);
-    float nq = 0.f;
-#pragma unroll
-    for (int i = 0; i < ND; ++i) {
-      nv[i] = fmaf(a, nv[i], b * k[i]);
-      nq = fmaf(nv[i], q[i], nq);
-    }
-    nq = warp_sum(nq);
-    if (lane == 0) {
-      float* c = coef + ((size_t)t * H + h) * 4;
-      c[0] = a;
-      c[1] = b;
-      c[2] = fmaxf(fabsf(nq), expf(-m_new)) + 1e-6f;
-    }
-    m = m_new;
-    if (t + 1 < t1) {
-#pragma unroll
-      for (int i = 0; i < ND; ++i) { q[i] = qn[i]; k[i] = kn[i]; }
-      gi = gin;
-      gf = gfn;
-    }
+    __syncthreads();
   }
+  if (warp != 0) return;
 #pragma unroll
   for (int i = 0; i < ND; ++i)
     if (lane + 32 * i < D) st[lane + 32 * i] = nv[i];
   if (lane == 0) st[D] = m;
 }
 
-// The matrix memory itself: a warp owns CW columns of one head's S (no other warp touches them), lane l rows l,
-// l + 32, ...; per token S' = a S + (b k) v^T and o = S'^T q / denominator, with a, b and the denominator from coef.
+// The matrix memory itself: a block takes SCAN_WARPS * CW columns of one head's S, a warp CW of them (no other warp
+// touches them), lane l rows l, l + 32, ...; per token S' = a S + (b k) v^T and o = S'^T q / denominator, with a, b
+// and the denominator from coef.
 template <int ND>
 __global__ void __launch_bounds__(SCAN_WARPS * 32)
 mlstm_scan_kernel(const float* __restrict__ x, int N, const int* __restrict__ slot, const int* __restrict__ seq_start,
                   int n_seq, float* __restrict__ state, long long state_stride, const float* __restrict__ coef,
-                  float* __restrict__ out, int H, int D, int V, int col_groups) {
+                  float* __restrict__ out, int H, int D, int V, int col_blocks) {
+  constexpr int BC = SCAN_WARPS * CW;    // columns per block
+  extern __shared__ float sm[];
+  float* q_s = sm;                       // [TCH][D]
+  float* k_s = q_s + TCH * D;            // [TCH][D]
+  float* v_s = k_s + TCH * D;            // [TCH][BC]
+  float* c_s = v_s + TCH * BC;           // [TCH][4]: decay, intake, denominator
   pdl_launch();
   pdl_wait();
-  const int lane = threadIdx.x & 31;
-  const long long item = (long long)blockIdx.x * SCAN_WARPS + (threadIdx.x >> 5);
-  if (item >= (long long)n_seq * H * col_groups) return;
-  const int cg = (int)(item % col_groups), h = (int)((item / col_groups) % H), e = (int)(item / ((long long)col_groups * H));
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int cb = blockIdx.x % col_blocks, h = (blockIdx.x / col_blocks) % H, e = blockIdx.x / (col_blocks * H);
   const int t0 = seq_start ? seq_start[e] : e, t1 = seq_start ? seq_start[e + 1] : e + 1;
   if (t1 <= t0) return;
   float* st = state + (size_t)slot[t0] * state_stride + (size_t)h * ((size_t)D * V + D + 1);
-  const int c0 = cg * CW;
+  const int c0 = cb * BC + warp * CW;
   float Sm[CW][ND];
 #pragma unroll
   for (int i = 0; i < ND; ++i) {
@@ -141,54 +170,45 @@ mlstm_scan_kernel(const float* __restrict__ x, int N, const int* __restrict__ sl
 #pragma unroll
     for (int c = 0; c < CW; ++c) Sm[c][i] = (d < D && c0 + c < V) ? st[(size_t)(c0 + c) * D + d] : 0.f;
   }
-  const int oq = h * D, ok = H * D + h * D, ov = 2 * H * D + h * V + c0;
-  float q[ND], k[ND], v[CW], a, b, den;
-  auto fetch = [&](int t, float* qq, float* kk, float* vv, float& aa, float& bb, float& dd) {
-    const float* row = x + (size_t)t * N;
+  const int oq = h * D, ok = H * D + h * D, ov = 2 * H * D + h * V + cb * BC;
+  for (int tc = t0; tc < t1; tc += TCH) {
+    const int n = min(TCH, t1 - tc);
+    stage_tokens(x, N, tc, n, oq, ok, D, q_s, k_s, [&] {
+      for (int j = threadIdx.x; j < n * BC; j += blockDim.x)
+        v_s[j] = cb * BC + j % BC < V ? x[(size_t)(tc + j / BC) * N + ov + j % BC] : 0.f;
+      for (int j = threadIdx.x; j < n * 4; j += blockDim.x) c_s[j] = coef[((size_t)(tc + (j >> 2)) * H + h) * 4 + (j & 3)];
+    });
+    __syncthreads();
+    if (c0 < V) {
+#pragma unroll 2
+      for (int j = 0; j < n; ++j) {
+        const float a = c_s[4 * j], b = c_s[4 * j + 1], den = c_s[4 * j + 2];
+        float v[CW], acc[CW];
 #pragma unroll
-    for (int i = 0; i < ND; ++i) {
-      const int d = lane + 32 * i;
-      qq[i] = d < D ? row[oq + d] : 0.f;
-      kk[i] = d < D ? row[ok + d] : 0.f;
-    }
+        for (int c = 0; c < CW; ++c) {
+          v[c] = v_s[j * BC + warp * CW + c];
+          acc[c] = 0.f;
+        }
 #pragma unroll
-    for (int c = 0; c < CW; ++c) vv[c] = c0 + c < V ? row[ov + c] : 0.f;
-    const float* cf = coef + ((size_t)t * H + h) * 4;
-    aa = cf[0];
-    bb = cf[1];
-    dd = cf[2];
-  };
-  fetch(t0, q, k, v, a, b, den);
-  for (int t = t0; t < t1; ++t) {
-    float qn[ND], kn[ND], vn[CW], an = 0.f, bn = 0.f, dn = 1.f;
-    if (t + 1 < t1) fetch(t + 1, qn, kn, vn, an, bn, dn);
-    float acc[CW];
+        for (int i = 0; i < ND; ++i) {
+          const int d = lane + 32 * i;
+          const float kd = d < D ? k_s[j * D + d] : 0.f, qd = d < D ? q_s[j * D + d] : 0.f;
+          const float bk = b * kd;
 #pragma unroll
-    for (int c = 0; c < CW; ++c) acc[c] = 0.f;
+          for (int c = 0; c < CW; ++c) {
+            Sm[c][i] = fmaf(a, Sm[c][i], bk * v[c]);
+            acc[c] = fmaf(Sm[c][i], qd, acc[c]);
+          }
+        }
 #pragma unroll
-    for (int i = 0; i < ND; ++i) {
-      const float bk = b * k[i];
+        for (int c = 0; c < CW; ++c) acc[c] = warp_sum(acc[c]);
+        float mine = acc[0];
 #pragma unroll
-      for (int c = 0; c < CW; ++c) {
-        Sm[c][i] = fmaf(a, Sm[c][i], bk * v[c]);
-        acc[c] = fmaf(Sm[c][i], q[i], acc[c]);
+        for (int c = 1; c < CW; ++c) mine = lane == c ? acc[c] : mine;
+        if (lane < CW && c0 + lane < V) out[((size_t)(tc + j) * H + h) * V + c0 + lane] = mine / den;
       }
     }
-#pragma unroll
-    for (int c = 0; c < CW; ++c) acc[c] = warp_sum(acc[c]);
-    float mine = acc[0];
-#pragma unroll
-    for (int c = 1; c < CW; ++c) mine = lane == c ? acc[c] : mine;
-    if (lane < CW && c0 + lane < V) out[((size_t)t * H + h) * V + c0 + lane] = mine / den;
-    if (t + 1 < t1) {
-#pragma unroll
-      for (int i = 0; i < ND; ++i) { q[i] = qn[i]; k[i] = kn[i]; }
-#pragma unroll
-      for (int c = 0; c < CW; ++c) v[c] = vn[c];
-      a = an;
-      b = bn;
-      den = dn;
-    }
+    __syncthreads();
   }
 #pragma unroll
   for (int i = 0; i < ND; ++i) {
@@ -249,16 +269,18 @@ extern "C" int flint_mlstm_scan(const float* x, const int* slot, const int* seq_
   if (state_stride < (long long)H * ((long long)D * V + D + 1)) return fail("mlstm_scan: the state rows are too short");
   if (!seq_start && n_seq != T) return fail("mlstm_scan: without a list of starts every request brings one row");
   const int N = 2 * H * D + 2 * H * V + 2 * H;
-  const int col_groups = (V + CW - 1) / CW;
-  const long long gate_items = (long long)n_seq * H, items = gate_items * col_groups;
-  const dim3 gate_grid((unsigned)((gate_items + SCAN_WARPS - 1) / SCAN_WARPS));
-  const dim3 grid((unsigned)((items + SCAN_WARPS - 1) / SCAN_WARPS)), block(SCAN_WARPS * 32);
+  const int col_blocks = (V + SCAN_WARPS * CW - 1) / (SCAN_WARPS * CW);
+  const long long gate_blocks = (long long)n_seq * H, blocks = gate_blocks * col_blocks;
+  if (blocks > 0x7fffffffLL) return fail("mlstm_scan: too many work items");
+  const dim3 gate_grid((unsigned)gate_blocks), grid((unsigned)blocks), block(SCAN_WARPS * 32);
+  const size_t gate_smem = (size_t)(2 * TCH * D + 2 * TCH) * sizeof(float);
+  const size_t smem = (size_t)(2 * TCH * D + TCH * SCAN_WARPS * CW + 4 * TCH) * sizeof(float);
 #define SCAN(ND)                                                                                                     \
   do {                                                                                                               \
-    launch_pdl(mlstm_gate_scan_kernel<ND>, gate_grid, block, 0, stream, x, N, slot, seq_start, n_seq, state,         \
+    launch_pdl(mlstm_gate_scan_kernel<ND>, gate_grid, block, gate_smem, stream, x, N, slot, seq_start, n_seq, state, \
                state_stride, coef, H, D, V);                                                                         \
-    launch_pdl(mlstm_scan_kernel<ND>, grid, block, 0, stream, x, N, slot, seq_start, n_seq, state, state_stride,     \
-               (const float*)coef, out, H, D, V, col_groups);                                                        \
+    launch_pdl(mlstm_scan_kernel<ND>, grid, block, smem, stream, x, N, slot, seq_start, n_seq, state, state_stride,  \
+               (const float*)coef, out, H, D, V, col_blocks);                                                        \
   } while (0)
   if (D <= 32) SCAN(1);
   else if (D <= 64) SCAN(2);

@@ -386,28 +386,8 @@ router_sigmoid_kernel(const float* __restrict__ x, const TW* __restrict__ wr, in
     if (logits_out)
       for (int e = lane; e < R; e += 32) logits_out[(size_t)t * R + e] = zr[e];
     __syncwarp();
-    for (int e = lane; e < R; e += 32) zr[e] = 1.0f / (1.0f + expf(-zr[e]));
-    __syncwarp();
-    for (int c = 0; c < top; ++c) {
-      float val = -1.f;
-      int idx = 0x7fffffff;
-      for (int e = lane; e < E; e += 32)
-        if (zr[e] > val) { val = zr[e]; idx = e; }
-#pragma unroll
-      for (int o = 16; o > 0; o >>= 1) {
-        const float ov = __shfl_xor_sync(0xffffffffu, val, o);
-        const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
-        if (ov > val || (ov == val && oi < idx)) { val = ov; idx = oi; }
-      }
-      if (lane == 0) {
-        expert_ids[(size_t)t * top + c] = idx;
-        scores[(size_t)t * top + c] = val;
-        weights[(size_t)t * (top + X) + c] = 1.0f;
-        zr[idx] = -2.f;                       // taken
-      }
-      __syncwarp();
-    }
-    for (int e = lane; e < X; e += 32) weights[(size_t)t * (top + X) + top + e] = zr[E + e];
+    select_sigmoid_by_warp(zr, lane, E, X, top, expert_ids + (size_t)t * top, scores + (size_t)t * top,
+                           weights + (size_t)t * (top + X));
   }
 }
 

@@ -252,6 +252,7 @@ class CudaOps:
         wr = logits = None
         E, jit, ids, gates = 0, 0.0, None, None
         r_top, r_groups, r_keep, r_scale = 0, 1, 1, 1.0
+        r_rule, r_extra, r_aux = 0, 0, None
         if router is not None:
             wr, E, jit, ids, gates = router.weight, router.weight.shape[0], router.jitter_eps, router.expert_ids, router.gates
             logits = getattr(router, "logits", None)
@@ -264,11 +265,17 @@ class CudaOps:
             _check(wr, "router weight", dims=2)
             if wr.shape[1] != H or ids.numel() != (r_top or 2) * T or gates.numel() != (r_top or 2) * T:
                 raise KernelError("row_norm: router shapes do not match")
+            if getattr(router, "rule", "") == "sigmoid":
+                r_rule, r_extra, r_aux = 1, int(router.extra), router.weights
+                _check(r_aux, "router weights out", torch.float32, 2)
+                if tuple(r_aux.shape) != (T, r_top + r_extra) or r_top < 1:
+                    raise KernelError(f"row_norm: the sigmoid router's weights must be [{T}, {r_top + r_extra}]")
         self._run("row_fused", "flint_row_norm", _ptr(x), _ptr(row_index), c_int(rows), c_int(H), _ptr(partials),
                   c_int(S), c_longlong(stride), _ptr(bias), _ptr(y), _ptr(row_of), _ptr(gts), c_int(top), _ptr(gamma), _ptr(beta),
                   c_float(eps), c_int({"layer": 0, "rms": 1}[mode]), _ptr(out_f32), _ptr(out_bf16), _ptr(wr),
                   c_int(_code(wr.dtype) if wr is not None else 0), c_int(E), c_float(jit), _ptr(ids), _ptr(gates),
-                  _ptr(logits), c_int(r_top), c_int(r_groups), c_int(r_keep), c_float(r_scale))
+                  _ptr(logits), c_int(r_top), c_int(r_groups), c_int(r_keep), c_float(r_scale), c_int(r_rule), c_int(r_extra),
+                  _ptr(r_aux))
 
     def apply_pending(self, x, pending):
         """x += what a part left pending (for a norm that cannot take it along)."""
@@ -1010,6 +1017,9 @@ class CudaOps:
 
     def route(self, x, router):
         """Serve a ``RouterRequest`` on normalised rows x [T, H] float32 with the stand-alone kernels."""
+        if getattr(router, "rule", "") == "sigmoid":
+            return self.router_sigmoid(x, router.weight, router.weight.shape[0] - router.extra, router.top, router.expert_ids,
+                                       router.gates, router.weights, getattr(router, "logits", None))
         if int(getattr(router, "top", 0)) > 0:
             return self.router_topk(x, router.weight, router.top, router.groups, router.keep, router.scale,
                                     router.expert_ids, router.gates, getattr(router, "logits", None))

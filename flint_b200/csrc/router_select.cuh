@@ -99,4 +99,34 @@ __device__ __forceinline__ void select_topk_by_warp(float* s, int lane, int E, i
   }
 }
 
+// The choice of a sigmoid router, by one warp, from float32 logits in shared memory: scores sigmoid(logit) over the
+// first E entries, the `top` largest chosen (the lower index among equals), their scores given as they are.  The
+// `extra` entries after them are gates of always-on parts: weights [top + extra] gets 1 for every chosen expert
+// and the sigmoids of those entries.  `s` holds the logits on entry and is overwritten.
+__device__ __forceinline__ void select_sigmoid_by_warp(float* s, int lane, int E, int extra, int top, int* ids,
+                                                       float* scores, float* weights) {
+  for (int e = lane; e < E + extra; e += 32) s[e] = 1.0f / (1.0f + expf(-s[e]));
+  __syncwarp();
+  for (int c = 0; c < top; ++c) {
+    float val = -1.f;
+    int idx = 0x7fffffff;
+    for (int e = lane; e < E; e += 32)
+      if (s[e] > val) { val = s[e]; idx = e; }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, val, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+      if (ov > val || (ov == val && oi < idx)) { val = ov; idx = oi; }
+    }
+    if (lane == 0) {
+      ids[c] = idx;
+      scores[c] = val;
+      weights[c] = 1.0f;
+      s[idx] = -2.f;                          // taken
+    }
+    __syncwarp();
+  }
+  for (int e = lane; e < extra; e += 32) weights[top + e] = s[E + e];
+}
+
 }  // namespace flint

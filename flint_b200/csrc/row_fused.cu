@@ -32,6 +32,7 @@ struct RowArgs {
   float* out_f32; __nv_bfloat16* out_bf16;
   const void* wr; int E; float jitter_eps; int* expert_ids; float* gates;
   int top, n_groups, keep; float out_scale;      // top > 0: the softmax router limited to groups instead of sparsemixer
+  int rule, extra; float* aux;  // rule 1: the sigmoid router (scores into gates, the last `extra` rows of wr are gates: aux)
   float* router_logits;        // optional [rows, E]: the logits the selection was made from (for tests)
   int H;
 };
@@ -279,8 +280,12 @@ row_norm_kernel(const __grid_constant__ RowArgs a) {
       if (a.router_logits) a.router_logits[(size_t)r * E + e] = t;
     }
     __syncwarp();
-    select_topk_by_warp(s, lane, E, a.top, a.n_groups, a.keep, a.out_scale, a.expert_ids + (size_t)a.top * r,
-                        a.gates + (size_t)a.top * r);
+    if (a.rule == 1)
+      select_sigmoid_by_warp(s, lane, E - a.extra, a.extra, a.top, a.expert_ids + (size_t)a.top * r,
+                             a.gates + (size_t)a.top * r, a.aux + (size_t)(a.top + a.extra) * r);
+    else
+      select_topk_by_warp(s, lane, E, a.top, a.n_groups, a.keep, a.out_scale, a.expert_ids + (size_t)a.top * r,
+                          a.gates + (size_t)a.top * r);
     return;
   }
   if (E <= 32) {
@@ -522,8 +527,12 @@ row_norm_cluster_kernel(const __grid_constant__ RowArgs a, const int vec_per_blo
       if (a.router_logits) a.router_logits[(size_t)r * E + e] = t;
     }
     __syncwarp();
-    select_topk_by_warp(s, lane, E, a.top, a.n_groups, a.keep, a.out_scale, a.expert_ids + (size_t)a.top * r,
-                        a.gates + (size_t)a.top * r);
+    if (a.rule == 1)
+      select_sigmoid_by_warp(s, lane, E - a.extra, a.extra, a.top, a.expert_ids + (size_t)a.top * r,
+                             a.gates + (size_t)a.top * r, a.aux + (size_t)(a.top + a.extra) * r);
+    else
+      select_topk_by_warp(s, lane, E, a.top, a.n_groups, a.keep, a.out_scale, a.expert_ids + (size_t)a.top * r,
+                          a.gates + (size_t)a.top * r);
     return;
   }
   if (E <= 32) {
@@ -597,21 +606,28 @@ extern "C" int flint_row_norm_set_cluster_rows(int rows) {
 // gamma NULL: only apply the pending additions.  wr != NULL (router weights [E, H], bf16 or f32):
 // also fill expert_ids [rows, 2] and gates [rows, 2] (and router_logits [rows, E] if given); then row_index
 // must be NULL.  top > 0: the router is a softmax limited to groups (`keep` of `n_groups`, `top` experts, gates times
-// out_scale) and expert_ids and gates are [rows, top]; top == 0: sparsemixer top-2.
+// out_scale) and expert_ids and gates are [rows, top]; top == 0: sparsemixer top-2.  rule 1: a sigmoid router over the
+// first E - extra rows of wr (the `top` largest scores, given as they are in gates); the last `extra` rows are gates of
+// always-on parts, and aux [rows, top + extra] gets 1 for the chosen experts and those rows' sigmoids.
 extern "C" int flint_row_norm(float* x, const int* row_index, int rows, int H, const float* partials,
                               int n_partials, long long partial_stride, const float* add_bias,
                               const float* comb_y, const int* comb_row_of, const float* comb_gates, int comb_top,
                               const float* gamma, const float* beta, float eps, int mode, float* out_f32,
                               void* out_bf16, const void* wr, int w_dtype, int E, float jitter_eps,
                               int* expert_ids, float* gates, float* router_logits, int top, int n_groups, int keep,
-                              float out_scale, cudaStream_t stream) {
+                              float out_scale, int rule, int extra, float* aux, cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (H <= 0 || (H & 3) || H > 4 * 1024 * MAX_VPT) return fail("row_norm: width %d (multiples of 4 up to %d)", H, 4096 * MAX_VPT);
   if (gamma && !out_f32 && !out_bf16 && !wr) return fail("row_norm: no output given");
   if (mode != 0 && mode != 1) return fail("row_norm: unknown mode %d", mode);
   if (comb_y && comb_top < 1) return fail("row_norm: %d expert rows a token", comb_top);
   if (wr && (E < (top > 0 ? 1 : 2) || E > MAX_E)) return fail("row_norm: %d experts (up to %d)", E, MAX_E);
-  if (wr && top > 0 && (top > ROUTER_MAX_TOP || top > E || n_groups < 1 || n_groups > 64 || E % n_groups || keep < 1 ||
+  if (wr && rule == 1) {
+    if (top < 1 || top > ROUTER_MAX_TOP || extra < 0 || top > E - extra || !aux)
+      return fail("row_norm: a sigmoid router choosing %d of %d experts (%d gate rows) is not supported", top, E - extra, extra);
+  } else if (wr && rule != 0) {
+    return fail("row_norm: unknown router rule %d", rule);
+  } else if (wr && top > 0 && (top > ROUTER_MAX_TOP || top > E || n_groups < 1 || n_groups > 64 || E % n_groups || keep < 1 ||
                         keep > n_groups || keep * (E / n_groups) < top))
     return fail("row_norm: %d of %d experts from %d of %d groups is not supported", top, E, keep, n_groups);
   if (wr && (row_index || !gamma || !expert_ids || !gates)) return fail("row_norm: the router needs a norm and all rows");
@@ -625,6 +641,7 @@ extern "C" int flint_row_norm(float* x, const int* row_index, int rows, int H, c
   a.wr = wr; a.E = E; a.jitter_eps = jitter_eps; a.expert_ids = expert_ids; a.gates = gates;
   a.top = wr ? top : 0; a.n_groups = n_groups; a.keep = keep; a.out_scale = out_scale;
   a.router_logits = wr ? router_logits : nullptr;
+  a.rule = wr ? rule : 0; a.extra = extra; a.aux = aux;
   a.H = H;
   const int n4 = H / 4;
   // a handful of rows: a cluster of blocks per row

@@ -58,8 +58,10 @@ class RouterRequest:
     ``weight`` [E, H] and the choice of experts, into ``expert_ids`` and ``gates`` ([T, k] each).  The rule is
     sparsemixer top-2 with ``jitter_eps`` (``top`` 0), or, with ``top`` > 0, a softmax whose choice is limited to
     the ``keep`` best of ``groups`` equal groups of neighbouring experts, ``top`` experts a token, gates times
-    ``scale``.  ``logits`` ([T, E] float32, optional): the logits the choice was made from are written there too
-    (tests compare them)."""
+    ``scale``.  With ``rule`` "sigmoid": scores sigmoid(logit) over the first rows of ``weight``, the ``top`` largest
+    chosen, ``gates`` their scores as they are; the last ``extra`` rows of ``weight`` are gates of always-on parts,
+    and ``weights`` [T, top + extra] gets 1 for every chosen expert and those rows' sigmoids.  ``logits`` ([T, E]
+    float32, optional): the logits the choice was made from are written there too (tests compare them)."""
     weight: torch.Tensor
     jitter_eps: float
     expert_ids: torch.Tensor
@@ -69,6 +71,9 @@ class RouterRequest:
     groups: int = 1
     keep: int = 1
     scale: float = 1.0
+    rule: str = ""
+    extra: int = 0
+    weights: torch.Tensor | None = None
 
 
 @dataclass

@@ -270,17 +270,30 @@ class SigmoidTopKMoE(FeedForward):
     def input_dtypes(self):
         return (torch.float32, self.w_up.dtype)       # the router reads the float32 rows
 
+    def router_request(self, n_rows):
+        """Routing can ride on the norm before this part (the normalised row is in registers there)."""
+        dev, k, extra = self.w_router.device, self.top, 1 if self.shared else 0
+        return RouterRequest(self.w_router, 0.0, torch.empty((n_rows, k), dtype=torch.int32, device=dev),
+                             torch.empty((n_rows, k), dtype=torch.float32, device=dev), top=k, rule="sigmoid", extra=extra,
+                             weights=torch.empty((n_rows, k + extra), dtype=torch.float32, device=dev))
+
+    def input_dtypes_when_routed(self):
+        return (self.w_up.dtype,)
+
     def forward(self, x, residual, step, routed=None):
         ops = self.ops
         xa = x[self.w_up.dtype]
         T, dev, k, extra = xa.shape[0], xa.device, self.top, 1 if self.shared else 0
-        ids = torch.empty((T, k), dtype=torch.int32, device=dev)
-        scores = torch.empty((T, k), dtype=torch.float32, device=dev)
-        # what the pending rows are weighted by when they are added: 1 for the experts (their score went into
-        # their input), the sigmoid gate for the shared expert
-        weights = torch.empty((T, k + extra), dtype=torch.float32, device=dev)
-        logits = torch.empty((T, self.E + extra), dtype=torch.float32, device=dev) if step.record is not None else None
-        ops.router_sigmoid(x[torch.float32], self.w_router, self.E, k, ids, scores, weights, logits)
+        if routed is not None:
+            # what the pending rows are weighted by when they are added: 1 for the experts (their score went into
+            # their input), the sigmoid gate for the shared expert
+            ids, scores, weights, logits = routed.expert_ids, routed.gates, routed.weights, routed.logits
+        else:
+            ids = torch.empty((T, k), dtype=torch.int32, device=dev)
+            scores = torch.empty((T, k), dtype=torch.float32, device=dev)
+            weights = torch.empty((T, k + extra), dtype=torch.float32, device=dev)
+            logits = torch.empty((T, self.E + extra), dtype=torch.float32, device=dev) if step.record is not None else None
+            ops.router_sigmoid(x[torch.float32], self.w_router, self.E, k, ids, scores, weights, logits)
         plan, xs = ops.moe_dispatch(ids, self.E, ops.moe_tile_rows(T, self.E, self.w_up.dtype, k), xa)
         a = torch.empty((k * T, self.inter), dtype=self.w_up.dtype, device=dev)
         ops.row_act(ops.gemm_partials(xs, self.w_up, plan=plan), a, self.act, row_of=plan.row_of, row_scale=scores)

@@ -261,6 +261,35 @@ def test_sigmoid_router(ops, wdtype, E, top, extra):
         assert (weights.cpu().double()[:, top] - torch.sigmoid(x.double() @ w[E].double())).abs().max() < 1e-5
 
 
+@pytest.mark.parametrize("wdtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("T,H", [(41, 72), (5, 2048), (300, 2048)])     # a block a row; a cluster of blocks a row; many rows
+@pytest.mark.parametrize("E,top,extra", [(16, 1, 1), (5, 2, 0), (64, 6, 1)])
+def test_sigmoid_router_rides_on_the_norm(ops, wdtype, T, H, E, top, extra):
+    """The norm's kernel fills a routing request for the sigmoid rule: the same experts, scores and gate as the plain
+    rule on the plain norm (scale stored as an offset from one) of the rows."""
+    from flint_b200.parts.base import RouterRequest
+    g = torch.Generator().manual_seed(T + E)
+    x = torch.randn(T, H, generator=g)
+    offset = 0.1 * torch.randn(H, generator=g)
+    wr = (torch.randn(E + extra, H, generator=g) * (3.0 / math.sqrt(H))).to(wdtype)
+    req = RouterRequest(wr.to(DEV), 0.0, torch.zeros(T, top, dtype=torch.int32, device=DEV), torch.zeros(T, top, device=DEV),
+                        logits=torch.zeros(T, E + extra, device=DEV), top=top, rule="sigmoid", extra=extra,
+                        weights=torch.zeros(T, top + extra, device=DEV))
+    out = torch.zeros(T, H, dtype=torch.bfloat16, device=DEV)
+    ops.row_norm(x.clone().to(DEV), (1.0 + offset).to(DEV), None, 1e-5, "rms", out_bf16=out, router=req)
+    n = P.offset_rms_norm(x.double(), offset.double(), 1e-5)
+    assert (out.cpu().double() - n).abs().max() < 3e-2
+    idx, val, z = P.sigmoid_router(n, {"r.router": wr[:E].double()}, "r.", top)
+    assert (req.logits.cpu().double()[:, :E] - z).abs().max() < 2e-4
+    same = int((req.expert_ids.cpu().long() == idx).all(-1).sum())
+    assert same >= T - 2                        # elsewhere two scores are within rounding of each other
+    rows = (req.expert_ids.cpu().long() == idx).all(-1)
+    assert (req.gates.cpu().double()[rows] - val[rows]).abs().max() < 1e-4
+    assert torch.all(req.weights.cpu()[:, :top] == 1.0)
+    if extra:
+        assert (req.weights.cpu().double()[:, top] - torch.sigmoid(n @ wr[E].double())).abs().max() < 1e-4
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_expert_activation_with_scores_and_the_clamped_gated_unit(ops, dtype):
     g = torch.Generator().manual_seed(5)
