@@ -158,6 +158,7 @@ sink_attention_kernel(const TQ* __restrict__ q, const TC* __restrict__ k_cache, 
     if (row >= 0) {
       const TC* kr = k_cache + row * hd;
       if (k_vec) {
+#pragma unroll 4
         for (int d = 0; d < hd; d += 8) {
           float kf[8];
           Vec8<TC>::load(kr + d, kf);
@@ -191,21 +192,32 @@ sink_attention_kernel(const TQ* __restrict__ q, const TC* __restrict__ k_cache, 
       for (int i = 0; i < MAX_DPL; ++i) acc[g][i] *= alpha;
     }
     const int nk = min(32, u_hi - u0);
-    for (int jj = 0; jj < nk; ++jj) {
-      const long long vrow = __shfl_sync(0xffffffffu, row, jj);
-      float pj[GC];
+    constexpr int VU = 4;      // value rows in flight per lane
+    for (int jj0 = 0; jj0 < nk; jj0 += VU) {
+      float vv[VU][MAX_DPL];
 #pragma unroll
-      for (int g = 0; g < GC; ++g) pj[g] = __shfl_sync(0xffffffffu, pr[g], jj);
-      if (vrow < 0) continue;
-      const TC* vr = v_cache + vrow * vd;
+      for (int u = 0; u < VU; ++u) {
+        const long long vrow = __shfl_sync(0xffffffffu, row, (jj0 + u) & 31);
+        const bool ok = jj0 + u < nk && vrow >= 0;
+        const TC* vr = v_cache + (ok ? vrow : 0) * vd;
 #pragma unroll
-      for (int i = 0; i < MAX_DPL; ++i) {
-        const int d = lane + 32 * i;
-        if (i < dpl && d < vd) {
-          const float vv = to_f32(vr[d]);
-#pragma unroll
-          for (int g = 0; g < GC; ++g) acc[g][i] = fmaf(pj[g], vv, acc[g][i]);
+        for (int i = 0; i < MAX_DPL; ++i) {
+          const int d = lane + 32 * i;
+          vv[u][i] = (ok && i < dpl && d < vd) ? to_f32(vr[d]) : 0.f;
         }
+      }
+#pragma unroll
+      for (int u = 0; u < VU; ++u) {
+        float pj[GC];
+#pragma unroll
+        for (int g = 0; g < GC; ++g) pj[g] = __shfl_sync(0xffffffffu, pr[g], (jj0 + u) & 31);
+        if (jj0 + u >= nk) continue;          // the same for every lane
+#pragma unroll
+        for (int i = 0; i < MAX_DPL; ++i)
+          if (i < dpl) {
+#pragma unroll
+            for (int g = 0; g < GC; ++g) acc[g][i] = fmaf(pj[g], vv[u][i], acc[g][i]);
+          }
       }
     }
   }

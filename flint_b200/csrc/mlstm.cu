@@ -9,8 +9,9 @@
 // f = logsigmoid(cap tanh((z_f + b_f) / cap)); it is parallel over tokens.  flint_mlstm_scan walks the tokens of
 // every request in order, in two kernels: one warp per (request, head) carries m and n and leaves every token's
 // decay, intake and denominator; then a warp per CW columns of one head's S (lane l holds rows l, l + 32, ... of
-// each) carries those columns, so no warp touches another's part of the state; a block stages the operands of 16
-// tokens at a time in shared memory, so the walk does not wait for global memory at every token.  The state is read from and written back to the request's row of the state slab
+// each) carries those columns, so no warp touches another's part of the state; a block stages the operands of eight
+// tokens at a time in shared memory by asynchronous copies, two stages alternating, so the walk does not wait
+// for global memory.  The state is read from and written back to the request's row of the state slab
 // (per head: S transposed [V, D], then n [D], then m), so a prompt cut anywhere gives the same numbers.
 // flint_mlstm_finish divides each head's o by its root mean square and applies the scale and the output gate.
 //
@@ -24,34 +25,36 @@ using namespace flint;
 
 namespace {
 
-constexpr int CW = 4;          // columns of S per warp
-constexpr int SCAN_WARPS = 4;  // warps per block of the scan
-constexpr int TCH = 16;        // tokens staged in shared memory at a time
+constexpr int CW = 2;          // columns of S per warp
+constexpr int SCAN_WARPS = 8;  // warps per block of the scan: two to a scheduler hide each other's latencies
+constexpr int TCH = 8;         // tokens staged in shared memory at a time (two such stages alternate); at most 32
+static_assert(TCH * CW <= 32 && SCAN_WARPS * 32 >= 256, "the gate scan gives a lane a token and a thread a dim (up to 256)");
 
 // Both scans walk a request's tokens one after the other, and what they read of a token does not depend on the
 // token before.  A block therefore brings the operands of TCH tokens into shared memory with all its threads
-// (q and k of the head, and whatever `more` adds), and the recurrence then runs on those without waiting for
-// global memory at every token.
+// (q and k of the head, and whatever `more` adds) by asynchronous copies, into one of two stages, while the
+// recurrence runs on the other: the walk never waits for global memory at a token.
+__device__ __forceinline__ void copy4(float* dst, const float* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void copies_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int PENDING>
+__device__ __forceinline__ void copies_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(PENDING) : "memory"); }
+
 template <typename More>
 __device__ __forceinline__ void stage_tokens(const float* __restrict__ x, int N, int t_first, int n, int oq, int ok, int D,
                                              float* q_s, float* k_s, More more) {
-  // a thread takes dims d, d + blockDim.x, ... of every staged token; the loads of all TCH tokens are in flight
-  // together (one after the other they would each cost a trip to L2)
   for (int d = threadIdx.x; d < D; d += blockDim.x) {
-    float tq[TCH], tk[TCH];
     const float* col = x + (size_t)t_first * N + d;
 #pragma unroll
-    for (int j = 0; j < TCH; ++j) {
-      tq[j] = j < n ? col[(size_t)j * N + oq] : 0.f;
-      tk[j] = j < n ? col[(size_t)j * N + ok] : 0.f;
-    }
-#pragma unroll
-    for (int j = 0; j < TCH; ++j) {
-      q_s[j * D + d] = tq[j];
-      k_s[j * D + d] = tk[j];
-    }
+    for (int j = 0; j < TCH; ++j)
+      if (j < n) {
+        copy4(q_s + j * D + d, col + (size_t)j * N + oq);
+        copy4(k_s + j * D + d, col + (size_t)j * N + ok);
+      }
   }
   more();
+  copies_commit();
 }
 
 __device__ __forceinline__ float log_sigmoid(float z) { return fminf(z, 0.f) - log1pf(expf(-fabsf(z))); }
@@ -78,67 +81,91 @@ __global__ void mlstm_prepare_kernel(const float* __restrict__ partials, int S, 
 }
 
 // The part of the recurrence that all columns of a head share: m, n and the denominator.  One block per (request,
-// head); its first warp walks the request's tokens and leaves, per token, the decay e^(f + m - m'), the intake
-// e^(i - m') and the denominator max(|n' . q|, e^(-m')) + 1e-6 in coef [T, H, 4]; it alone reads and writes n and
-// m of the state.
-template <int ND>
+// head), one thread per dim of n (D <= blockDim).  Per staged chunk: every thread walks the short chain of maxima;
+// lanes 0 .. TCH - 1 of each warp take a token each and make its decay e^(f + m - m'), intake e^(i - m') and
+// e^(-m') (shared by shuffle); every thread carries its dim of n through the chunk; the partial dot products n' . q
+// of all tokens are summed side by side over the warp, then over the warps in a fixed order.  The block leaves decay,
+// intake and the denominator max(|n' . q|, e^(-m')) + 1e-6 per token in coef [T, H, 4]; it alone touches n and m.
 __global__ void __launch_bounds__(SCAN_WARPS * 32)
 mlstm_gate_scan_kernel(const float* __restrict__ x, int N, const int* __restrict__ slot, const int* __restrict__ seq_start,
                        int n_seq, float* __restrict__ state, long long state_stride, float* __restrict__ coef, int H,
                        int D, int V) {
   extern __shared__ float sm[];
-  float* q_s = sm;                       // [TCH][D]
-  float* k_s = q_s + TCH * D;            // [TCH][D]
-  float* g_s = k_s + TCH * D;            // [TCH][2]: log input gate, log forget gate
+  const int stage_floats = 2 * TCH * D + 2 * TCH;       // per stage: q [TCH][D], k [TCH][D], log gates [TCH][2]
+  __shared__ float part[SCAN_WARPS][TCH];
   pdl_launch();
   pdl_wait();
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, d = threadIdx.x;
   const int h = blockIdx.x % H, e = blockIdx.x / H;
   const int t0 = seq_start ? seq_start[e] : e, t1 = seq_start ? seq_start[e + 1] : e + 1;
   if (t1 <= t0) return;
   float* st = state + (size_t)slot[t0] * state_stride + (size_t)h * ((size_t)D * V + D + 1) + (size_t)D * V;
-  float nv[ND];
-#pragma unroll
-  for (int i = 0; i < ND; ++i) nv[i] = (warp == 0 && lane + 32 * i < D) ? st[lane + 32 * i] : 0.f;
+  float nv = d < D ? st[d] : 0.f;
   float m = st[D];
   const int oq = h * D, ok = H * D + h * D, oi = 2 * H * D + 2 * H * V + h;
-  for (int tc = t0; tc < t1; tc += TCH) {
+  auto stage = [&](int tc, int which) {
+    float* q_s = sm + which * stage_floats;
+    float* g_s = q_s + 2 * TCH * D;
     const int n = min(TCH, t1 - tc);
-    stage_tokens(x, N, tc, n, oq, ok, D, q_s, k_s, [&] {
-      for (int j = threadIdx.x; j < 2 * n; j += blockDim.x) g_s[j] = x[(size_t)(tc + (j >> 1)) * N + oi + (j & 1) * H];
+    stage_tokens(x, N, tc, n, oq, ok, D, q_s, q_s + TCH * D, [&] {
+      for (int j = threadIdx.x; j < 2 * n; j += blockDim.x) copy4(g_s + j, x + (size_t)(tc + (j >> 1)) * N + oi + (j & 1) * H);
     });
-    __syncthreads();
-    if (warp == 0) {
-      for (int j = 0; j < n; ++j) {
-        const float gi = g_s[2 * j], gf = g_s[2 * j + 1];
-        const float m_new = fmaxf(gf + m, gi);
-        const float a = expf(gf + m - m_new), b = expf(gi - m_new);
-        float nq = 0.f;
-#pragma unroll
-        for (int i = 0; i < ND; ++i) {
-          const int d = lane + 32 * i;
-          if (d < D) {
-            nv[i] = fmaf(a, nv[i], b * k_s[j * D + d]);
-            nq = fmaf(nv[i], q_s[j * D + d], nq);
-          }
-        }
-        nq = warp_sum(nq);
-        if (lane == 0) {
-          float* c = coef + ((size_t)(tc + j) * H + h) * 4;
-          c[0] = a;
-          c[1] = b;
-          c[2] = fmaxf(fabsf(nq), expf(-m_new)) + 1e-6f;
-        }
-        m = m_new;
-      }
+  };
+  stage(t0, 0);
+  int which = 0;
+  for (int tc = t0; tc < t1; tc += TCH, which ^= 1) {
+    const int n = min(TCH, t1 - tc);
+    if (tc + TCH < t1) {
+      stage(tc + TCH, which ^ 1);
+      copies_wait<1>();
+    } else {
+      copies_wait<0>();
     }
     __syncthreads();
-  }
-  if (warp != 0) return;
+    const float* q_s = sm + which * stage_floats;
+    const float* k_s = q_s + TCH * D;
+    const float* g_s = k_s + TCH * D;
+    // the maxima: m before and after the token this lane takes (lanes TCH and up idle along)
+    float m_before = m, m_after = m, gi_mine = 0.f, gf_mine = 0.f;
 #pragma unroll
-  for (int i = 0; i < ND; ++i)
-    if (lane + 32 * i < D) st[lane + 32 * i] = nv[i];
-  if (lane == 0) st[D] = m;
+    for (int j = 0; j < TCH; ++j)
+      if (j < n) {
+        const float gi = g_s[2 * j], gf = g_s[2 * j + 1];
+        const float m_new = fmaxf(gf + m, gi);
+        if (lane == j) { m_before = m; m_after = m_new; gi_mine = gi; gf_mine = gf; }
+        m = m_new;
+      }
+    const float a_mine = expf(gf_mine + m_before - m_after), b_mine = expf(gi_mine - m_after), em_mine = expf(-m_after);
+    float pq[TCH];
+#pragma unroll
+    for (int j = 0; j < TCH; ++j) {
+      const float a = __shfl_sync(0xffffffffu, a_mine, j), b = __shfl_sync(0xffffffffu, b_mine, j);
+      pq[j] = 0.f;
+      if (j < n && d < D) {
+        nv = fmaf(a, nv, b * k_s[j * D + d]);
+        pq[j] = nv * q_s[j * D + d];
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < TCH; ++j) pq[j] = warp_sum(pq[j]);
+    if (lane == 0) {
+#pragma unroll
+      for (int j = 0; j < TCH; ++j) part[warp][j] = pq[j];
+    }
+    __syncthreads();
+    if (warp == 0 && lane < n) {
+      float nq = 0.f;
+#pragma unroll
+      for (int w = 0; w < SCAN_WARPS; ++w) nq += part[w][lane];       // fixed order
+      float* c = coef + ((size_t)(tc + lane) * H + h) * 4;
+      c[0] = a_mine;
+      c[1] = b_mine;
+      c[2] = fmaxf(fabsf(nq), em_mine) + 1e-6f;
+    }
+    __syncthreads();          // the stage just read is refilled two chunks on, `part` by the next chunk
+  }
+  if (d < D) st[d] = nv;
+  if (threadIdx.x == 0) st[D] = m;
 }
 
 // The matrix memory itself: a block takes SCAN_WARPS * CW columns of one head's S, a warp CW of them (no other warp
@@ -151,10 +178,7 @@ mlstm_scan_kernel(const float* __restrict__ x, int N, const int* __restrict__ sl
                   float* __restrict__ out, int H, int D, int V, int col_blocks) {
   constexpr int BC = SCAN_WARPS * CW;    // columns per block
   extern __shared__ float sm[];
-  float* q_s = sm;                       // [TCH][D]
-  float* k_s = q_s + TCH * D;            // [TCH][D]
-  float* v_s = k_s + TCH * D;            // [TCH][BC]
-  float* c_s = v_s + TCH * BC;           // [TCH][4]: decay, intake, denominator
+  const int stage_floats = 2 * TCH * D + TCH * BC + 4 * TCH;   // per stage: q, k [TCH][D], v [TCH][BC], coef [TCH][4]
   pdl_launch();
   pdl_wait();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -171,44 +195,73 @@ mlstm_scan_kernel(const float* __restrict__ x, int N, const int* __restrict__ sl
     for (int c = 0; c < CW; ++c) Sm[c][i] = (d < D && c0 + c < V) ? st[(size_t)(c0 + c) * D + d] : 0.f;
   }
   const int oq = h * D, ok = H * D + h * D, ov = 2 * H * D + h * V + cb * BC;
-  for (int tc = t0; tc < t1; tc += TCH) {
+  // columns beyond the head's last have the value 0 in both stages, once and for all
+  for (int j = threadIdx.x; j < 2 * TCH * BC; j += blockDim.x)
+    if (cb * BC + j % BC >= V) sm[(j / (TCH * BC)) * stage_floats + 2 * TCH * D + j % (TCH * BC)] = 0.f;
+  auto stage = [&](int tc, int which) {
+    float* q_s = sm + which * stage_floats;
+    float* v_s = q_s + 2 * TCH * D;
+    float* c_s = v_s + TCH * BC;
     const int n = min(TCH, t1 - tc);
-    stage_tokens(x, N, tc, n, oq, ok, D, q_s, k_s, [&] {
+    stage_tokens(x, N, tc, n, oq, ok, D, q_s, q_s + TCH * D, [&] {
       for (int j = threadIdx.x; j < n * BC; j += blockDim.x)
-        v_s[j] = cb * BC + j % BC < V ? x[(size_t)(tc + j / BC) * N + ov + j % BC] : 0.f;
-      for (int j = threadIdx.x; j < n * 4; j += blockDim.x) c_s[j] = coef[((size_t)(tc + (j >> 2)) * H + h) * 4 + (j & 3)];
+        if (cb * BC + j % BC < V) copy4(v_s + j, x + (size_t)(tc + j / BC) * N + ov + j % BC);
+      for (int j = threadIdx.x; j < n * 4; j += blockDim.x) copy4(c_s + j, coef + ((size_t)(tc + (j >> 2)) * H + h) * 4 + (j & 3));
     });
-    __syncthreads();
-    if (c0 < V) {
-#pragma unroll 2
-      for (int j = 0; j < n; ++j) {
-        const float a = c_s[4 * j], b = c_s[4 * j + 1], den = c_s[4 * j + 2];
-        float v[CW], acc[CW];
-#pragma unroll
-        for (int c = 0; c < CW; ++c) {
-          v[c] = v_s[j * BC + warp * CW + c];
-          acc[c] = 0.f;
-        }
-#pragma unroll
-        for (int i = 0; i < ND; ++i) {
-          const int d = lane + 32 * i;
-          const float kd = d < D ? k_s[j * D + d] : 0.f, qd = d < D ? q_s[j * D + d] : 0.f;
-          const float bk = b * kd;
-#pragma unroll
-          for (int c = 0; c < CW; ++c) {
-            Sm[c][i] = fmaf(a, Sm[c][i], bk * v[c]);
-            acc[c] = fmaf(Sm[c][i], qd, acc[c]);
-          }
-        }
-#pragma unroll
-        for (int c = 0; c < CW; ++c) acc[c] = warp_sum(acc[c]);
-        float mine = acc[0];
-#pragma unroll
-        for (int c = 1; c < CW; ++c) mine = lane == c ? acc[c] : mine;
-        if (lane < CW && c0 + lane < V) out[((size_t)(tc + j) * H + h) * V + c0 + lane] = mine / den;
-      }
+  };
+  stage(t0, 0);
+  int which = 0;
+  for (int tc = t0; tc < t1; tc += TCH, which ^= 1) {
+    const int n = min(TCH, t1 - tc);
+    if (tc + TCH < t1) {
+      stage(tc + TCH, which ^ 1);
+      copies_wait<1>();
+    } else {
+      copies_wait<0>();
     }
     __syncthreads();
+    const float* q_s = sm + which * stage_floats;
+    const float* k_s = q_s + TCH * D;
+    const float* v_s = k_s + TCH * D;
+    const float* c_s = v_s + TCH * BC;
+    if (c0 < V) {
+      // the chunk's tokens one after the other through S (a chain of one multiply-add a token and element); the
+      // sums over the warp of all tokens and columns then run side by side, and lane j CW + c writes token j's column c
+      float acc[TCH][CW];
+#pragma unroll
+      for (int j = 0; j < TCH; ++j) {
+#pragma unroll
+        for (int c = 0; c < CW; ++c) acc[j][c] = 0.f;
+        if (j < n) {
+          const float a = c_s[4 * j], b = c_s[4 * j + 1];
+          float v[CW];
+#pragma unroll
+          for (int c = 0; c < CW; ++c) v[c] = v_s[j * BC + warp * CW + c];
+#pragma unroll
+          for (int i = 0; i < ND; ++i) {
+            const int d = lane + 32 * i;
+            const float kd = d < D ? k_s[j * D + d] : 0.f, qd = d < D ? q_s[j * D + d] : 0.f;
+            const float bk = b * kd;
+#pragma unroll
+            for (int c = 0; c < CW; ++c) {
+              Sm[c][i] = fmaf(a, Sm[c][i], bk * v[c]);
+              acc[j][c] = fmaf(Sm[c][i], qd, acc[j][c]);
+            }
+          }
+        }
+      }
+      float mine = 0.f;
+#pragma unroll
+      for (int j = 0; j < TCH; ++j)
+#pragma unroll
+        for (int c = 0; c < CW; ++c) {
+          const float t = warp_sum(acc[j][c]);
+          mine = lane == j * CW + c ? t : mine;
+        }
+      const int j = lane / CW, c = lane % CW;
+      if (j < n && c0 + c < V) out[((size_t)(tc + j) * H + h) * V + c0 + c] = mine / c_s[4 * j + 2];
+    }
+    __syncthreads();          // the stage just read is refilled two chunks on
   }
 #pragma unroll
   for (int i = 0; i < ND; ++i) {
@@ -273,11 +326,11 @@ extern "C" int flint_mlstm_scan(const float* x, const int* slot, const int* seq_
   const long long gate_blocks = (long long)n_seq * H, blocks = gate_blocks * col_blocks;
   if (blocks > 0x7fffffffLL) return fail("mlstm_scan: too many work items");
   const dim3 gate_grid((unsigned)gate_blocks), grid((unsigned)blocks), block(SCAN_WARPS * 32);
-  const size_t gate_smem = (size_t)(2 * TCH * D + 2 * TCH) * sizeof(float);
-  const size_t smem = (size_t)(2 * TCH * D + TCH * SCAN_WARPS * CW + 4 * TCH) * sizeof(float);
+  const size_t gate_smem = (size_t)2 * (2 * TCH * D + 2 * TCH) * sizeof(float);                      // two stages each
+  const size_t smem = (size_t)2 * (2 * TCH * D + TCH * SCAN_WARPS * CW + 4 * TCH) * sizeof(float);
 #define SCAN(ND)                                                                                                     \
   do {                                                                                                               \
-    launch_pdl(mlstm_gate_scan_kernel<ND>, gate_grid, block, gate_smem, stream, x, N, slot, seq_start, n_seq, state, \
+    launch_pdl(mlstm_gate_scan_kernel, gate_grid, block, gate_smem, stream, x, N, slot, seq_start, n_seq, state,     \
                state_stride, coef, H, D, V);                                                                         \
     launch_pdl(mlstm_scan_kernel<ND>, grid, block, smem, stream, x, N, slot, seq_start, n_seq, state, state_stride,  \
                (const float*)coef, out, H, D, V, col_blocks);                                                        \
