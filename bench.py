@@ -458,22 +458,22 @@ def gepadra_config(width, heads, kv_heads, dim, vdim, window, keep, rot, m_heads
     for i in range(layers):
         if i % every == every - 1:
             kind, m = "attention", {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "scale": dim ** -0.5,
-                                    "mask": {"size": window, "keep_first": keep}, "rot": {"dims": rot, "base": 1e6}, "v_mix": True}
+                                    "mask": {"size": window, "keep_first": keep}, "rot": {"dims": rot, "base": 5e5}, "v_mix": True}
         else:
             kind, m = "mlstm", {"heads": m_heads, "dim": m_dim, "vdim": m_vdim, "gate_cap": 15.0}
         mlp = {"kind": "dense", "ff": dense_ff, "limit": 7.0} if i == 0 else \
             {"kind": "moe", "expert": {"ff": ff}, "router": {"experts": experts, "top": top}, "shared": {"ff": shared}}
         out.append({"type": kind, "mixer": m, "mlp": mlp})
-    return {"architecture": "Gepadra", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "layers": out}
+    return {"architecture": "Gepadra", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "layers": out}
 
 
 # layer sizes that resemble real models of this kind, beside the Phi-MoE layer of equal width, head count and head size
 GEPADRA_SIZES = {
-    "2048x16": dict(width=2048, heads=16, kv_heads=4, dim=128, vdim=128, window=1024, keep=4, rot=64, m_heads=4, m_dim=256,
+    "2048x16": dict(width=2048, heads=16, kv_heads=4, dim=128, vdim=128, window=1024, keep=8, rot=64, m_heads=4, m_dim=256,
                     m_vdim=512, ff=2112, experts=16, top=2, shared=2112, dense_ff=5632,
                     phi=dict(hidden_size=2048, num_attention_heads=16, num_key_value_heads=4, head_dim=128,
                              intermediate_size=1408, num_local_experts=16)),
-    "4096x32": dict(width=4096, heads=32, kv_heads=8, dim=128, vdim=128, window=1024, keep=4, rot=64, m_heads=8, m_dim=256,
+    "4096x32": dict(width=4096, heads=32, kv_heads=8, dim=128, vdim=128, window=1024, keep=8, rot=64, m_heads=8, m_dim=256,
                     m_vdim=512, ff=1440, experts=16, top=2, shared=1440, dense_ff=8192,
                     phi=dict(hidden_size=4096, num_attention_heads=32, num_key_value_heads=8, head_dim=128,
                              intermediate_size=960, num_local_experts=16)),

@@ -102,8 +102,10 @@ __global__ void qkv_write_kernel(const float* __restrict__ qkv, int n_partials, 
 }
 
 // ------------------------------------------------------------------------------------------- attention
-template <typename TQ, typename TC, typename TO>
-__global__ void __launch_bounds__(WARPS * 32)
+// DPL: value dims a lane holds (vd <= 32 DPL); the narrow forms keep fewer registers, so more blocks fit an SM and
+// hide each other's waits for their key rows.
+template <typename TQ, typename TC, typename TO, int DPL>
+__global__ void __launch_bounds__(WARPS * 32, DPL <= 4 ? 6 : 3)
 sink_attention_kernel(const TQ* __restrict__ q, const TC* __restrict__ k_cache, const TC* __restrict__ v_cache,
                       const int* __restrict__ block_table, int max_pages, int page_size, const int* __restrict__ pos,
                       const int* __restrict__ slot, TO* __restrict__ out, float* __restrict__ scratch, int T, int nq,
@@ -135,13 +137,13 @@ sink_attention_kernel(const TQ* __restrict__ q, const TC* __restrict__ k_cache, 
 
   const bool k_vec = (hd % 8) == 0;
   const int dpl = (vd + 31) / 32;
-  float m[GC], l[GC], acc[GC][MAX_DPL];
+  float m[GC], l[GC], acc[GC][DPL];
 #pragma unroll
   for (int g = 0; g < GC; ++g) {
     m[g] = -INFINITY;
     l[g] = 0.f;
 #pragma unroll
-    for (int i = 0; i < MAX_DPL; ++i) acc[g][i] = 0.f;
+    for (int i = 0; i < DPL; ++i) acc[g][i] = 0.f;
   }
 
   for (int u0 = u_lo; u0 < u_hi; u0 += 32) {
@@ -158,7 +160,7 @@ sink_attention_kernel(const TQ* __restrict__ q, const TC* __restrict__ k_cache, 
     if (row >= 0) {
       const TC* kr = k_cache + row * hd;
       if (k_vec) {
-#pragma unroll 4
+#pragma unroll 2
         for (int d = 0; d < hd; d += 8) {
           float kf[8];
           Vec8<TC>::load(kr + d, kf);
@@ -189,19 +191,19 @@ sink_attention_kernel(const TQ* __restrict__ q, const TC* __restrict__ k_cache, 
       l[g] = l[g] * alpha + warp_sum(pr[g]);
       m[g] = m_new;
 #pragma unroll
-      for (int i = 0; i < MAX_DPL; ++i) acc[g][i] *= alpha;
+      for (int i = 0; i < DPL; ++i) acc[g][i] *= alpha;
     }
     const int nk = min(32, u_hi - u0);
     constexpr int VU = 4;      // value rows in flight per lane
     for (int jj0 = 0; jj0 < nk; jj0 += VU) {
-      float vv[VU][MAX_DPL];
+      float vv[VU][DPL];
 #pragma unroll
       for (int u = 0; u < VU; ++u) {
         const long long vrow = __shfl_sync(0xffffffffu, row, (jj0 + u) & 31);
         const bool ok = jj0 + u < nk && vrow >= 0;
         const TC* vr = v_cache + (ok ? vrow : 0) * vd;
 #pragma unroll
-        for (int i = 0; i < MAX_DPL; ++i) {
+        for (int i = 0; i < DPL; ++i) {
           const int d = lane + 32 * i;
           vv[u][i] = (ok && i < dpl && d < vd) ? to_f32(vr[d]) : 0.f;
         }
@@ -213,7 +215,7 @@ sink_attention_kernel(const TQ* __restrict__ q, const TC* __restrict__ k_cache, 
         for (int g = 0; g < GC; ++g) pj[g] = __shfl_sync(0xffffffffu, pr[g], (jj0 + u) & 31);
         if (jj0 + u >= nk) continue;          // the same for every lane
 #pragma unroll
-        for (int i = 0; i < MAX_DPL; ++i)
+        for (int i = 0; i < DPL; ++i)
           if (i < dpl) {
 #pragma unroll
             for (int g = 0; g < GC; ++g) acc[g][i] = fmaf(pj[g], vv[u][i], acc[g][i]);
@@ -234,7 +236,7 @@ sink_attention_kernel(const TQ* __restrict__ q, const TC* __restrict__ k_cache, 
         }
         const float inv = sum > 0.f ? scale_o / sum : 0.f;
 #pragma unroll
-        for (int i = 0; i < MAX_DPL; ++i) {
+        for (int i = 0; i < DPL; ++i) {
           const int d = lane + 32 * i;
           if (i < dpl && d < vd) out[((size_t)t * nq + h0 + g) * vd + d] = from_f32<TO>(acc[g][i] * inv);
         }
@@ -246,7 +248,7 @@ sink_attention_kernel(const TQ* __restrict__ q, const TC* __restrict__ k_cache, 
       if (g < ng) {
         float* dst = scratch + (((size_t)t * nq + h0 + g) * n_splits + split) * (vd + 2);
 #pragma unroll
-        for (int i = 0; i < MAX_DPL; ++i) {
+        for (int i = 0; i < DPL; ++i) {
           const int d = lane + 32 * i;
           if (i < dpl && d < vd) dst[d] = acc[g][i];
         }
@@ -329,11 +331,18 @@ extern "C" int flint_sink_attention(const void* q, int q_dtype, const void* k_ca
   const long long blocks = (items + WARPS - 1) / WARPS;
   if (blocks > 0x7fffffffLL) return fail("sink_attention: too many work items");
   const size_t smem = (size_t)WARPS * GC * hd * sizeof(float);
-#define LAUNCH(TQ, TC)                                                                                            \
-  launch_pdl(sink_attention_kernel<TQ, TC, TQ>, dim3((unsigned)blocks), dim3(WARPS * 32), smem, stream, (const TQ*)q, \
+#define LAUNCH_D(TQ, TC, DPL)                                                                                         \
+  launch_pdl(sink_attention_kernel<TQ, TC, TQ, DPL>, dim3((unsigned)blocks), dim3(WARPS * 32), smem, stream, (const TQ*)q, \
              (const TC*)k_cache, (const TC*)v_cache, block_table, max_pages, page_size, pos, slot, (TQ*)out, scratch, T, \
              nq, nkv, hd, vd, window, keep_first, sinks, scale, split_keys, n_splits, g_chunks)
+#define LAUNCH(TQ, TC)                                                     \
+  do {                                                                     \
+    if (vd <= 64) LAUNCH_D(TQ, TC, 2);                                     \
+    else if (vd <= 128) LAUNCH_D(TQ, TC, 4);                               \
+    else LAUNCH_D(TQ, TC, 8);                                              \
+  } while (0)
   FLINT_DISPATCH_DTYPE(q_dtype, TQ, FLINT_DISPATCH_DTYPE(cache_dtype, TC, LAUNCH(TQ, TC)));
+#undef LAUNCH_D
 #undef LAUNCH
   int rc = check_launch("sink_attention");
   if (rc || n_splits == 1) return rc;
