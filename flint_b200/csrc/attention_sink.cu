@@ -110,7 +110,7 @@ sink_attention_kernel(const TQ* __restrict__ q, const TC* __restrict__ k_cache, 
                       const int* __restrict__ block_table, int max_pages, int page_size, const int* __restrict__ pos,
                       const int* __restrict__ slot, TO* __restrict__ out, float* __restrict__ scratch, int T, int nq,
                       int nkv, int hd, int vd, int window, int keep_first, const float* __restrict__ sinks, float scale,
-                      int split_keys, int n_splits, int g_chunks) {
+                      int split_keys, int n_splits, int g_chunks, const int* __restrict__ row_list) {
   extern __shared__ float smem[];  // per warp: GC * hd floats of q
   pdl_launch();
   pdl_wait();
@@ -122,7 +122,8 @@ sink_attention_kernel(const TQ* __restrict__ q, const TC* __restrict__ k_cache, 
   const int gchunk = (int)(rest % g_chunks);
   rest /= g_chunks;
   const int kvh = (int)(rest % nkv);
-  const int t = (int)(rest / nkv);
+  const int ti = (int)(rest / nkv);                  // index into the rows this launch covers
+  const int t = row_list ? row_list[ti] : ti;        // row of the batch
   const int G = nq / nkv, g0 = gchunk * GC, ng = min(GC, G - g0), h0 = kvh * G + g0;
   const int p = pos[t];
   const int lo = window > 0 ? max(0, p + 1 - window) : 0;
@@ -246,7 +247,7 @@ sink_attention_kernel(const TQ* __restrict__ q, const TC* __restrict__ k_cache, 
 #pragma unroll
     for (int g = 0; g < GC; ++g)
       if (g < ng) {
-        float* dst = scratch + (((size_t)t * nq + h0 + g) * n_splits + split) * (vd + 2);
+        float* dst = scratch + (((size_t)ti * nq + h0 + g) * n_splits + split) * (vd + 2);
 #pragma unroll
         for (int i = 0; i < DPL; ++i) {
           const int d = lane + 32 * i;
@@ -263,10 +264,11 @@ sink_attention_kernel(const TQ* __restrict__ q, const TC* __restrict__ k_cache, 
 // Merge the splits of one (row, head) and add the sink: out = sum_s e^(m_s - M) o_s / (sum_s e^(m_s - M) l_s + e^(sink - M)).
 template <typename TO>
 __global__ void sink_combine_kernel(const float* __restrict__ scratch, TO* __restrict__ out, int vd, int n_splits, int nq,
-                                    const float* __restrict__ sinks) {
+                                    const float* __restrict__ sinks, const int* __restrict__ row_list) {
   pdl_launch();
   pdl_wait();
-  const size_t rh = blockIdx.x;   // row * nq + head
+  const size_t rh = blockIdx.x;   // (index of the row in this launch) * nq + head
+  const size_t out_rh = row_list ? (size_t)row_list[rh / nq] * nq + rh % nq : rh;
   const float* base = scratch + rh * n_splits * (vd + 2);
   const float sk = sinks ? sinks[rh % nq] : -INFINITY;
   float M = sk;
@@ -283,7 +285,209 @@ __global__ void sink_combine_kernel(const float* __restrict__ scratch, TO* __res
       const float ms = base[(size_t)s * (vd + 2) + vd];
       if (ms > -INFINITY) o += expf(ms - M) * base[(size_t)s * (vd + 2) + d];
     }
-    out[rh * vd + d] = from_f32<TO>(o * inv);
+    out[out_rh * vd + d] = from_f32<TO>(o * inv);
+  }
+}
+
+
+// ------------------------------------------------------------------------------------------- long portions on the tensor cores
+// Tiles of up to 64 consecutive rows of one request (bfloat16, head sizes in multiples of 16 up to 128): a block of four
+// warps takes a tile and a query head, a warp 16 rows.  The keys the tile's rows see between them (the kept first ones,
+// then from the first row's window start to the last row's position) are walked in tiles of 64: keys and values come
+// into shared memory by asynchronous 16-byte copies (rows padded by 16 bytes, so ldmatrix meets no bank twice),
+// S = Q K^T by mma.sync m16n8k16 with Q's fragments in registers, the mask (not later; near, or kept) and the online
+// softmax in float32 on the accumulator fragment, P as bfloat16 the A operand of O += P V with V through ldmatrix.trans.
+// The sink joins maximum and sum at the end.
+constexpr int MQ = 64, MK = 64;      // query rows a block, keys a tile
+
+__device__ __forceinline__ void ldsm4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm4t(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void mma16816(float* d, const uint32_t* a, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+               "{%0, %1, %2, %3};"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void copy16(void* dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&v);
+}
+
+// HDS: most k steps of 16 query/key dims; VDT: most tiles of 8 value dims
+template <int HDS, int VDT>
+__global__ void __launch_bounds__(128)
+sink_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_cache,
+                          const __nv_bfloat16* __restrict__ v_cache, const int* __restrict__ block_table, int max_pages,
+                          int page_size, const int* __restrict__ tiles, __nv_bfloat16* __restrict__ out, int nq, int nkv, int hd,
+                          int vd, int window, int keep_first, const float* __restrict__ sinks, float scale) {
+  extern __shared__ __align__(16) unsigned char sm_raw[];
+  const int ldk = hd + 8, ldv = vd + 8;
+  __nv_bfloat16* k_s = reinterpret_cast<__nv_bfloat16*>(sm_raw);      // [MK][ldk]; first holds the query tile
+  __nv_bfloat16* v_s = k_s + MK * ldk;                                 // [MK][ldv]
+  int* kpos = reinterpret_cast<int*>(v_s + MK * ldv);                  // [MK]: position of each key of the tile, or -1
+  pdl_launch();
+  pdl_wait();
+  const int tile = blockIdx.x / nq, h = blockIdx.x % nq, kvh = h / (nq / nkv);
+  const int row0 = tiles[4 * tile], n_rows = tiles[4 * tile + 1], slot = tiles[4 * tile + 2], p0 = tiles[4 * tile + 3];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, tq = lane & 3;
+  const int hd16 = hd / 16, vdt = vd / 8, chunks_k = hd / 8, chunks_v = vd / 8;
+  const int lm = lane >> 3, lr = lane & 7;                             // ldmatrix: this lane addresses row lr of matrix lm
+
+  for (int i = tid; i < MQ * chunks_k; i += 128) {
+    const int r = i / chunks_k, c = i % chunks_k;
+    uint4 val = make_uint4(0u, 0u, 0u, 0u);
+    if (r < n_rows) val = *reinterpret_cast<const uint4*>(q + ((size_t)(row0 + r) * nq + h) * hd + c * 8);
+    *reinterpret_cast<uint4*>(k_s + r * ldk + c * 8) = val;
+  }
+  __syncthreads();
+  uint32_t qf[HDS][4];
+#pragma unroll
+  for (int ks = 0; ks < HDS; ++ks)
+    if (ks < hd16) {
+      const __nv_bfloat16* src = k_s + (warp * 16 + (lm & 1) * 8 + lr) * ldk + ks * 16 + (lm >> 1) * 8;
+      ldsm4((uint32_t)__cvta_generic_to_shared(src), qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3]);
+    }
+  __syncthreads();          // the query tile's place is free for keys
+
+  const int p_last = p0 + n_rows - 1;
+  const int lo_first = window > 0 ? max(0, p0 + 1 - window) : 0;
+  const bool gap = window > 0 && lo_first > keep_first;               // kept keys and window do not touch
+  const int n_first = gap ? keep_first : 0, base = gap ? lo_first : 0;
+  const int total = n_first + (p_last + 1 - base);
+  const int* bt = block_table + (size_t)slot * max_pages;
+  const int r_lo = warp * 16 + g;                                      // this thread's two rows: r_lo and r_lo + 8
+  const int p_row[2] = {p0 + r_lo, p0 + r_lo + 8};
+  const bool row_ok[2] = {r_lo < n_rows, r_lo + 8 < n_rows};
+  float m_r[2] = {-INFINITY, -INFINITY}, l_r[2] = {0.f, 0.f};
+  float o[VDT][4];
+#pragma unroll
+  for (int nt = 0; nt < VDT; ++nt)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) o[nt][e] = 0.f;
+
+  for (int u0 = 0; u0 < total; u0 += MK) {
+    if (tid < MK) {
+      const int u = u0 + tid;
+      kpos[tid] = u < total ? (u < n_first ? u : base + (u - n_first)) : -1;
+    }
+    __syncthreads();
+    for (int i = tid; i < MK * chunks_k; i += 128) {
+      const int r = i / chunks_k, c = i % chunks_k, j = kpos[r];
+      const int page = j >= 0 ? bt[j / page_size] : -1;
+      __nv_bfloat16* dst = k_s + r * ldk + c * 8;
+      if (page >= 0) copy16(dst, k_cache + (((size_t)page * nkv + kvh) * page_size + j % page_size) * hd + c * 8);
+      else *reinterpret_cast<uint4*>(dst) = make_uint4(0u, 0u, 0u, 0u);
+    }
+    for (int i = tid; i < MK * chunks_v; i += 128) {
+      const int r = i / chunks_v, c = i % chunks_v, j = kpos[r];
+      const int page = j >= 0 ? bt[j / page_size] : -1;
+      __nv_bfloat16* dst = v_s + r * ldv + c * 8;
+      if (page >= 0) copy16(dst, v_cache + (((size_t)page * nkv + kvh) * page_size + j % page_size) * vd + c * 8);
+      else *reinterpret_cast<uint4*>(dst) = make_uint4(0u, 0u, 0u, 0u);
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();
+
+    float s[MK / 8][4];
+#pragma unroll
+    for (int nt = 0; nt < MK / 8; ++nt)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) s[nt][e] = 0.f;
+#pragma unroll
+    for (int ks = 0; ks < HDS; ++ks)
+      if (ks < hd16) {
+#pragma unroll
+        for (int np = 0; np < MK / 16; ++np) {
+          uint32_t b0, b1, b2, b3;
+          const __nv_bfloat16* src = k_s + (np * 16 + (lm >> 1) * 8 + lr) * ldk + ks * 16 + (lm & 1) * 8;
+          ldsm4((uint32_t)__cvta_generic_to_shared(src), b0, b1, b2, b3);
+          mma16816(s[2 * np], qf[ks], b0, b1);
+          mma16816(s[2 * np + 1], qf[ks], b2, b3);
+        }
+      }
+    // mask, scale, and this tile's maxima of the thread's two rows
+    float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int nt = 0; nt < MK / 8; ++nt)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int j = kpos[nt * 8 + 2 * tq + (e & 1)], rs = e >> 1, p = p_row[rs];
+        const bool ok = j >= 0 && row_ok[rs] && j <= p && (window == 0 || p - j < window || j < keep_first);
+        s[nt][e] = ok ? s[nt][e] * scale : -INFINITY;
+        mx[rs] = fmaxf(mx[rs], s[nt][e]);
+      }
+    float alpha[2];
+#pragma unroll
+    for (int rs = 0; rs < 2; ++rs) {
+      mx[rs] = fmaxf(mx[rs], __shfl_xor_sync(0xffffffffu, mx[rs], 1));
+      mx[rs] = fmaxf(mx[rs], __shfl_xor_sync(0xffffffffu, mx[rs], 2));
+      const float m_new = fmaxf(m_r[rs], mx[rs]);
+      alpha[rs] = m_new > -INFINITY ? expf(m_r[rs] - m_new) : 1.f;      // 0 while m_r is still -inf
+      m_r[rs] = m_new;
+    }
+    float sum[2] = {0.f, 0.f};
+#pragma unroll
+    for (int nt = 0; nt < MK / 8; ++nt)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int rs = e >> 1;
+        const float pv = s[nt][e] > -INFINITY ? expf(s[nt][e] - m_r[rs]) : 0.f;
+        s[nt][e] = pv;
+        sum[rs] += pv;
+      }
+#pragma unroll
+    for (int rs = 0; rs < 2; ++rs) {
+      sum[rs] += __shfl_xor_sync(0xffffffffu, sum[rs], 1);
+      sum[rs] += __shfl_xor_sync(0xffffffffu, sum[rs], 2);
+      l_r[rs] = l_r[rs] * alpha[rs] + sum[rs];
+    }
+#pragma unroll
+    for (int nt = 0; nt < VDT; ++nt) {
+      o[nt][0] *= alpha[0]; o[nt][1] *= alpha[0];
+      o[nt][2] *= alpha[1]; o[nt][3] *= alpha[1];
+    }
+#pragma unroll
+    for (int kk = 0; kk < MK / 16; ++kk) {
+      const uint32_t a[4] = {pack_bf16(s[2 * kk][0], s[2 * kk][1]), pack_bf16(s[2 * kk][2], s[2 * kk][3]),
+                             pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]), pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3])};
+#pragma unroll
+      for (int vp = 0; vp < VDT / 2; ++vp)
+        if (2 * vp < vdt) {
+          uint32_t b0, b1, b2, b3;
+          const __nv_bfloat16* src = v_s + (kk * 16 + (lm & 1) * 8 + lr) * ldv + vp * 16 + (lm >> 1) * 8;
+          ldsm4t((uint32_t)__cvta_generic_to_shared(src), b0, b1, b2, b3);
+          mma16816(o[2 * vp], a, b0, b1);
+          mma16816(o[2 * vp + 1], a, b2, b3);
+        }
+    }
+    __syncthreads();        // the tiles are overwritten by the next round
+  }
+
+#pragma unroll
+  for (int rs = 0; rs < 2; ++rs) {
+    if (!row_ok[rs]) continue;
+    float so = 1.f, sum = l_r[rs];
+    if (sinks) {
+      const float sk = sinks[h], m_all = fmaxf(m_r[rs], sk);
+      so = m_r[rs] > -INFINITY ? expf(m_r[rs] - m_all) : 0.f;
+      sum = l_r[rs] * so + expf(sk - m_all);
+    }
+    const float inv = sum > 0.f ? so / sum : 0.f;
+    __nv_bfloat16* dst = out + ((size_t)(row0 + r_lo + 8 * rs) * nq + h) * vd + 2 * tq;
+#pragma unroll
+    for (int nt = 0; nt < VDT; ++nt)
+      if (nt < vdt)
+        *reinterpret_cast<uint32_t*>(dst + nt * 8) = pack_bf16(o[nt][2 * rs] * inv, o[nt][2 * rs + 1] * inv);
   }
 }
 
@@ -309,12 +513,12 @@ extern "C" int flint_qkv_write(const float* qkv, int n_partials, long long parti
 }
 
 // `scratch` must hold T * nq * n_splits * (vd + 2) floats when n_splits > 1; split_keys * n_splits must cover the
-// most keys any row sees.
+// most keys any row sees.  With a row list, T counts the listed rows and row_list[i] is the batch row of the i-th.
 extern "C" int flint_sink_attention(const void* q, int q_dtype, const void* k_cache, const void* v_cache, int cache_dtype,
                                     const int* block_table, int max_pages, int page_size, const int* pos,
                                     const int* slot, void* out, int T, int nq, int nkv, int hd, int vd, int window,
                                     int keep_first, const float* sinks, float scale, int split_keys, int n_splits,
-                                    float* scratch, cudaStream_t stream) {
+                                    float* scratch, const int* row_list, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (hd < 1 || vd < 1 || hd > 256 || vd > 32 * MAX_DPL)
     return fail("sink_attention: head sizes %d (keys) and %d (values) are not supported (1 to 256)", hd, vd);
@@ -334,7 +538,7 @@ extern "C" int flint_sink_attention(const void* q, int q_dtype, const void* k_ca
 #define LAUNCH_D(TQ, TC, DPL)                                                                                         \
   launch_pdl(sink_attention_kernel<TQ, TC, TQ, DPL>, dim3((unsigned)blocks), dim3(WARPS * 32), smem, stream, (const TQ*)q, \
              (const TC*)k_cache, (const TC*)v_cache, block_table, max_pages, page_size, pos, slot, (TQ*)out, scratch, T, \
-             nq, nkv, hd, vd, window, keep_first, sinks, scale, split_keys, n_splits, g_chunks)
+             nq, nkv, hd, vd, window, keep_first, sinks, scale, split_keys, n_splits, g_chunks, row_list)
 #define LAUNCH(TQ, TC)                                                     \
   do {                                                                     \
     if (vd <= 64) LAUNCH_D(TQ, TC, 2);                                     \
@@ -349,8 +553,32 @@ extern "C" int flint_sink_attention(const void* q, int q_dtype, const void* k_ca
   const int threads = vd >= 128 ? 128 : 64;
   FLINT_DISPATCH_DTYPE(q_dtype, TO,
       (launch_pdl(sink_combine_kernel<TO>, dim3((unsigned)((long long)T * nq)), dim3(threads), 0, stream,
-                  (const float*)scratch, (TO*)out, vd, n_splits, nq, sinks)));
+                  (const float*)scratch, (TO*)out, vd, n_splits, nq, sinks, row_list)));
   return check_launch("sink_combine");
+}
+
+// tiles [n_tiles, 4] int32: first row, rows (up to 64), request slot, position of the first row; bfloat16 q, cache and
+// out; head sizes in multiples of 16 up to 128.
+extern "C" int flint_sink_attention_tiles(const void* q, const void* k_cache, const void* v_cache, const int* block_table,
+                                          int max_pages, int page_size, const int* tiles, int n_tiles, void* out, int nq,
+                                          int nkv, int hd, int vd, int window, int keep_first, const float* sinks,
+                                          float scale, cudaStream_t stream) {
+  if (n_tiles <= 0) return 0;
+  if (hd < 16 || vd < 16 || hd % 16 || vd % 16 || hd > 128 || vd > 128)
+    return fail("sink_attention_tiles: head sizes %d and %d (multiples of 16 up to 128)", hd, vd);
+  if (nkv <= 0 || nq % nkv) return fail("sink_attention_tiles: %d query heads do not divide into %d kv heads", nq, nkv);
+  if (window < 0 || keep_first < 0 || page_size <= 0) return fail("sink_attention_tiles: bad window or page size");
+  if ((long long)n_tiles * nq > 0x7fffffffLL) return fail("sink_attention_tiles: too many work items");
+  const size_t smem = (size_t)MK * ((hd + 8) + (vd + 8)) * 2 + MK * sizeof(int);
+  const dim3 grid((unsigned)(n_tiles * nq)), block(128);
+  const __nv_bfloat16 *qq = (const __nv_bfloat16*)q, *kk = (const __nv_bfloat16*)k_cache, *vv = (const __nv_bfloat16*)v_cache;
+  if (hd <= 64 && vd <= 64)
+    launch_pdl(sink_attention_mma_kernel<4, 8>, grid, block, smem, stream, qq, kk, vv, block_table, max_pages, page_size, tiles,
+               (__nv_bfloat16*)out, nq, nkv, hd, vd, window, keep_first, sinks, scale);
+  else
+    launch_pdl(sink_attention_mma_kernel<8, 16>, grid, block, smem, stream, qq, kk, vv, block_table, max_pages, page_size, tiles,
+               (__nv_bfloat16*)out, nq, nkv, hd, vd, window, keep_first, sinks, scale);
+  return check_launch("sink_attention_tiles");
 }
 
 extern "C" const char* flint_attention_sink_last_error() { return g_error; }

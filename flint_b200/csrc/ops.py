@@ -793,10 +793,14 @@ class CudaOps:
         keys = -(-(-(-span // n)) // 32) * 32
         return keys, -(-span // keys)
 
-    def sink_attention(self, q, cache, step, out, nq, nkv, hd, vd, window, keep_first, sinks, scale, splits=None):
+    def sink_attention(self, q, cache, step, out, nq, nkv, hd, vd, window, keep_first, sinks, scale, splits=None,
+                       tiling=None, rows=None):
         """Every row over its request's cached keys [.., hd] and values [.., vd]: row at position p sees key j if
         j <= p and (p - j < window or j < keep_first) (window 0: all); ``sinks`` [nq] float32 (or None): a logit
-        per query head that joins the softmax's denominator.  q [T, nq hd] -> out [T, nq vd]."""
+        per query head that joins the softmax's denominator.  q [T, nq hd] -> out [T, nq vd].  ``tiling``: the step's
+        rows cut into tiles of up to 64 rows (``engine.step.Tiling``): in bfloat16, with head sizes in multiples of
+        16 up to 128, the tiles run on the tensor cores and only the rows in no tile row by row.  ``rows``: int32
+        list of the batch rows to compute (default: all)."""
         _check(q, "q", dims=2)
         _check(out, "out", q.dtype, 2)
         T = q.shape[0]
@@ -809,6 +813,19 @@ class CudaOps:
             _check(sinks, "sinks", torch.float32, 1)
             if sinks.numel() != nq:
                 raise KernelError(f"sink_attention: sinks must have {nq} entries")
+        if (tiling is not None and tiling.n_tiles > 0 and rows is None and splits is None
+                and self.sink_attention_tiles_ok(q.dtype, cache.k.dtype, hd, vd)):
+            _check(tiling.tiles, "tiles", torch.int32)
+            self._run("attention_sink", "flint_sink_attention_tiles", _ptr(q), _ptr(cache.k), _ptr(cache.v),
+                      _ptr(cache.block_table), c_int(cache.block_table.shape[1]), c_int(P), _ptr(tiling.tiles),
+                      c_int(tiling.n_tiles), _ptr(out), c_int(nq), c_int(nkv), c_int(hd), c_int(vd), c_int(window),
+                      c_int(keep_first), _ptr(sinks), c_float(scale))
+            if not tiling.n_other_rows:
+                return
+            rows = tiling.other_rows
+        if rows is not None:
+            _check(rows, "rows", torch.int32, 1)
+            T = rows.numel()
         span = min(step.max_kv_len, window + keep_first) if window else step.max_kv_len
         keys, n = splits if splits is not None else self.sink_attention_plan(T, nq, nkv, span)
         if keys * n < span:
@@ -817,7 +834,15 @@ class CudaOps:
         self._run("attention_sink", "flint_sink_attention", _ptr(q), c_int(_code(q.dtype)), _ptr(cache.k), _ptr(cache.v),
                   c_int(_code(cache.k.dtype)), _ptr(cache.block_table), c_int(cache.block_table.shape[1]), c_int(P),
                   _ptr(step.pos), _ptr(step.slot), _ptr(out), c_int(T), c_int(nq), c_int(nkv), c_int(hd), c_int(vd),
-                  c_int(window), c_int(keep_first), _ptr(sinks), c_float(scale), c_int(keys), c_int(n), _ptr(scratch))
+                  c_int(window), c_int(keep_first), _ptr(sinks), c_float(scale), c_int(keys), c_int(n), _ptr(scratch),
+                  _ptr(rows))
+
+    @staticmethod
+    def sink_attention_tiles_ok(q_dtype, cache_dtype, hd, vd):
+        """Whether tiles of rows can run on the tensor cores: bfloat16 rows and cache, head sizes in multiples of 16
+        up to 128."""
+        return (q_dtype == torch.bfloat16 and cache_dtype == torch.bfloat16 and hd % 16 == 0 and vd % 16 == 0
+                and 16 <= hd <= 128 and 16 <= vd <= 128)
 
     # ------------------------------------------------------------------ matrix memory (mLSTM)
     def mlstm_scan(self, proj, b_gates, slot, seq_start, n_seq, state, out, H, D, V, cap):

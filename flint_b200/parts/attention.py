@@ -45,6 +45,8 @@ class Attention(Mixer):
     graph_safe = True
     # portions of at least 16 rows go to the tensor-core attention in tiles of 128 query rows, the rest row by row
     NEEDS = StepNeeds(tile_rows=128, tile_min_rows=16)
+    # the general kernels' tensor-core form takes tiles of 64 rows
+    NEEDS_GENERAL = StepNeeds(tile_rows=64, tile_min_rows=16)
 
     def __init__(self, params, ctx):
         super().__init__(params, ctx)
@@ -120,7 +122,11 @@ class Attention(Mixer):
         return KVSpec(self.nkv, self.hd, self.window)
 
     def step_needs(self):
-        return None if self.general else self.NEEDS
+        if not self.general:
+            return self.NEEDS
+        ok = getattr(self.ops, "sink_attention_tiles_ok", None)
+        tiles = ok is not None and ok(self.ctx.act_dtype, self.ctx.act_dtype, self.hd, self.vd)
+        return self.NEEDS_GENERAL if tiles else None
 
     def plan_step(self, step, captured):
         """How the key ranges of a batch of decoded tokens are cut.  Requests of about the same length share one
@@ -172,7 +178,9 @@ class Attention(Mixer):
         ops.qkv_write(qkv, self.b_qkv, step.pos, step.slot, self.cos, self.sin, self.rot, self.rot_style, q, cache,
                       nq, nkv, hd, vd, step.status, v_keep=v_keep, v_from=v_from, blend=self.blend)
         attn = torch.empty((T, nq * vd), dtype=act, device=dev)
-        ops.sink_attention(q, cache, step, attn, nq, nkv, hd, vd, self.window, self.keep_first, self.sink, self.scale)
+        needs = self.step_needs()
+        ops.sink_attention(q, cache, step, attn, nq, nkv, hd, vd, self.window, self.keep_first, self.sink, self.scale,
+                           tiling=step.tiling(needs) if needs is not None and q.dtype == torch.bfloat16 else None)
         return Pending(partials=ops.gemm_partials(attn, self.w_o), bias=self.b_o)
 
     def forward(self, x, residual, step, cache, state, writes_cache=True):

@@ -246,7 +246,8 @@ class RefOps:
         cache.k[pages, :, p % P, :] = k.to(cache.k.dtype)
         cache.v[pages, :, p % P, :] = v.to(cache.v.dtype)
 
-    def sink_attention(self, q, cache, step, out, nq, nkv, hd, vd, window, keep_first, sinks, scale, splits=None):
+    def sink_attention(self, q, cache, step, out, nq, nkv, hd, vd, window, keep_first, sinks, scale, splits=None,
+                       tiling=None, rows=None):
         T, P, G = q.shape[0], cache.page_size, nq // nkv
         qq = q.to(self.cd).view(T, nq, hd)
         res = torch.zeros(T, nq, vd, dtype=self.cd)

@@ -126,6 +126,46 @@ def test_sink_attention_finds_planted_keys(ops, dtype, H, G, d, dv, window, keep
     assert (out.cpu().double().view(2, H, dv) - want).abs().max().item() < (2e-5 if dtype == torch.float32 else 3e-2)
 
 
+@pytest.mark.parametrize("H,G,d,dv", [(4, 2, 32, 16), (8, 8, 128, 48), (6, 2, 64, 128), (2, 1, 16, 64)])
+@pytest.mark.parametrize("window,keep", [(40, 4), (9, 3), (0, 0), (100, 70), (33, 0)])
+def test_sink_attention_tiles_on_the_tensor_cores(ops, H, G, d, dv, window, keep):
+    """Portions of prompts as tiles of up to 64 rows (whole tiles, a ragged last one, a portion that starts in the
+    middle of a request and of a page, a portion just past the kept tokens) beside single rows, two requests: the
+    tensor-core kernel and the row kernel together against the plain mechanism, with peaked scores."""
+    from flint_b200.engine.step import Tiling
+    g = torch.Generator().manual_seed(H + d + window)
+    n, P_ = [333, 150], 16
+    keys = [2.0 * torch.randn(m, G, d, generator=g, dtype=F64) for m in n]
+    values = [torch.randn(m, G, dv, generator=g, dtype=F64) for m in n]
+    view, dense = paged_kv(keys, values, P_, torch.bfloat16, seed=3)
+    portions = [(0, 0, 150), (1, 0, 64), (0, 150, 17), (1, 64, 3), (0, 167, 166), (1, 67, 1), (1, 68, 82)]    # (slot, first position, count)
+    pos = [p0 + i for s_, p0, c in portions for i in range(c)]
+    slot = [s_ for s_, p0, c in portions for i in range(c)]
+    T = len(pos)
+    q = (2.0 * torch.randn(T, H, d, generator=g, dtype=F64)).to(torch.bfloat16)
+    sinks = torch.randn(H, generator=g) + 1.0
+    scale = d ** -0.5
+    tiles, others, row = [], [], 0
+    for s_, p0, c in portions:
+        if c < 16:
+            others += range(row, row + c)
+        else:
+            for r in range(0, c, 64):
+                tiles.append([row + r, min(64, c - r), s_, p0 + r])
+        row += c
+    tiles.sort(key=lambda t: -(t[3] + t[1]))
+    tiling = Tiling(torch.tensor(tiles, dtype=torch.int32, device=DEV), len(tiles), torch.tensor(others, dtype=torch.int32, device=DEV), len(others))
+    want = dense_attention(q, dense, pos, slot, H, G, scale, window, keep, sinks)
+    out = torch.zeros(T, H * dv, dtype=torch.bfloat16, device=DEV)
+    ops.sink_attention(q.reshape(T, H * d).to(DEV), view, step_of(pos, slot, len(portions)), out, H, G, d, dv, window, keep,
+                       sinks.to(DEV), scale, tiling=tiling)
+    err = (out.cpu().double().view(T, H, dv) - want).abs()
+    assert err.max().item() < 4e-2, (int(err.view(T, -1).max(-1).values.argmax()), err.max().item())
+    plain = torch.zeros_like(out)
+    ops.sink_attention(q.reshape(T, H * d).to(DEV), view, step_of(pos, slot, len(portions)), plain, H, G, d, dv, window, keep, sinks.to(DEV), scale)
+    assert (plain.float() - out.float()).abs().max().item() < 4e-2
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("style,rot", [("half", 12), ("half", 24), ("interleaved", 8), ("half", 0)])
 def test_qkv_write_rotates_blends_and_fills_the_pages(ops, dtype, style, rot):
