@@ -331,9 +331,9 @@ sink_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat
                           int vd, int window, int keep_first, const float* __restrict__ sinks, float scale) {
   extern __shared__ __align__(16) unsigned char sm_raw[];
   const int ldk = hd + 8, ldv = vd + 8;
-  __nv_bfloat16* k_s = reinterpret_cast<__nv_bfloat16*>(sm_raw);      // [MK][ldk]; first holds the query tile
-  __nv_bfloat16* v_s = k_s + MK * ldk;                                 // [MK][ldv]
-  int* kpos = reinterpret_cast<int*>(v_s + MK * ldv);                  // [MK]: position of each key of the tile, or -1
+  // two stages, each keys [MK][ldk], values [MK][ldv] and the keys' positions [MK] (or -1); the first stage's keys
+  // first hold the query tile
+  const int stage_bytes = MK * (ldk + ldv) * 2 + MK * (int)sizeof(int);
   pdl_launch();
   pdl_wait();
   const int tile = blockIdx.x / nq, h = blockIdx.x % nq, kvh = h / (nq / nkv);
@@ -342,18 +342,21 @@ sink_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat
   const int hd16 = hd / 16, vdt = vd / 8, chunks_k = hd / 8, chunks_v = vd / 8;
   const int lm = lane >> 3, lr = lane & 7;                             // ldmatrix: this lane addresses row lr of matrix lm
 
-  for (int i = tid; i < MQ * chunks_k; i += 128) {
-    const int r = i / chunks_k, c = i % chunks_k;
-    uint4 val = make_uint4(0u, 0u, 0u, 0u);
-    if (r < n_rows) val = *reinterpret_cast<const uint4*>(q + ((size_t)(row0 + r) * nq + h) * hd + c * 8);
-    *reinterpret_cast<uint4*>(k_s + r * ldk + c * 8) = val;
+  {
+    __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(sm_raw);
+    for (int i = tid; i < MQ * chunks_k; i += 128) {
+      const int r = i / chunks_k, c = i % chunks_k;
+      uint4 val = make_uint4(0u, 0u, 0u, 0u);
+      if (r < n_rows) val = *reinterpret_cast<const uint4*>(q + ((size_t)(row0 + r) * nq + h) * hd + c * 8);
+      *reinterpret_cast<uint4*>(q_s + r * ldk + c * 8) = val;
+    }
+    __syncthreads();
   }
-  __syncthreads();
   uint32_t qf[HDS][4];
 #pragma unroll
   for (int ks = 0; ks < HDS; ++ks)
     if (ks < hd16) {
-      const __nv_bfloat16* src = k_s + (warp * 16 + (lm & 1) * 8 + lr) * ldk + ks * 16 + (lm >> 1) * 8;
+      const __nv_bfloat16* src = reinterpret_cast<__nv_bfloat16*>(sm_raw) + (warp * 16 + (lm & 1) * 8 + lr) * ldk + ks * 16 + (lm >> 1) * 8;
       ldsm4((uint32_t)__cvta_generic_to_shared(src), qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3]);
     }
   __syncthreads();          // the query tile's place is free for keys
@@ -374,29 +377,45 @@ sink_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat
 #pragma unroll
     for (int e = 0; e < 4; ++e) o[nt][e] = 0.f;
 
-  for (int u0 = 0; u0 < total; u0 += MK) {
-    if (tid < MK) {
-      const int u = u0 + tid;
-      kpos[tid] = u < total ? (u < n_first ? u : base + (u - n_first)) : -1;
-    }
-    __syncthreads();
+  // the copies of one tile of keys and values into a stage; the next tile's are on their way while this one is worked
+  auto fetch = [&](int u0, int stage) {
+    __nv_bfloat16* k_d = reinterpret_cast<__nv_bfloat16*>(sm_raw + (size_t)stage * stage_bytes);
+    __nv_bfloat16* v_d = k_d + MK * ldk;
+    int* pos_d = reinterpret_cast<int*>(v_d + MK * ldv);
+    auto key_at = [&](int r) {
+      const int u = u0 + r;
+      return u < total ? (u < n_first ? u : base + (u - n_first)) : -1;
+    };
+    if (tid < MK) pos_d[tid] = key_at(tid);
     for (int i = tid; i < MK * chunks_k; i += 128) {
-      const int r = i / chunks_k, c = i % chunks_k, j = kpos[r];
+      const int r = i / chunks_k, c = i % chunks_k, j = key_at(r);
       const int page = j >= 0 ? bt[j / page_size] : -1;
-      __nv_bfloat16* dst = k_s + r * ldk + c * 8;
+      __nv_bfloat16* dst = k_d + r * ldk + c * 8;
       if (page >= 0) copy16(dst, k_cache + (((size_t)page * nkv + kvh) * page_size + j % page_size) * hd + c * 8);
       else *reinterpret_cast<uint4*>(dst) = make_uint4(0u, 0u, 0u, 0u);
     }
     for (int i = tid; i < MK * chunks_v; i += 128) {
-      const int r = i / chunks_v, c = i % chunks_v, j = kpos[r];
+      const int r = i / chunks_v, c = i % chunks_v, j = key_at(r);
       const int page = j >= 0 ? bt[j / page_size] : -1;
-      __nv_bfloat16* dst = v_s + r * ldv + c * 8;
+      __nv_bfloat16* dst = v_d + r * ldv + c * 8;
       if (page >= 0) copy16(dst, v_cache + (((size_t)page * nkv + kvh) * page_size + j % page_size) * vd + c * 8);
       else *reinterpret_cast<uint4*>(dst) = make_uint4(0u, 0u, 0u, 0u);
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
-    asm volatile("cp.async.wait_group 0;" ::: "memory");
+  };
+  fetch(0, 0);
+  int stage = 0;
+  for (int u0 = 0; u0 < total; u0 += MK, stage ^= 1) {
+    if (u0 + MK < total) {
+      fetch(u0 + MK, stage ^ 1);
+      asm volatile("cp.async.wait_group 1;" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+    }
     __syncthreads();
+    const __nv_bfloat16* k_s = reinterpret_cast<const __nv_bfloat16*>(sm_raw + (size_t)stage * stage_bytes);
+    const __nv_bfloat16* v_s = k_s + MK * ldk;
+    const int* kpos = reinterpret_cast<const int*>(v_s + MK * ldv);
 
     float s[MK / 8][4];
 #pragma unroll
@@ -415,24 +434,36 @@ sink_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat
           mma16816(s[2 * np + 1], qf[ks], b2, b3);
         }
       }
-    // mask, scale, and this tile's maxima of the thread's two rows
+    // mask, scale, and this tile's maxima of the thread's two rows.  Most tiles lie behind every row of the tile and
+    // inside every row's window: they need no mask
     float mx[2] = {-INFINITY, -INFINITY};
+    const bool interior = kpos[MK - 1] >= 0 && kpos[MK - 1] <= p0 && (window == 0 || p_last - kpos[0] < window);
+    if (interior) {
 #pragma unroll
-    for (int nt = 0; nt < MK / 8; ++nt)
+      for (int nt = 0; nt < MK / 8; ++nt)
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int j = kpos[nt * 8 + 2 * tq + (e & 1)], rs = e >> 1, p = p_row[rs];
-        const bool ok = j >= 0 && row_ok[rs] && j <= p && (window == 0 || p - j < window || j < keep_first);
-        s[nt][e] = ok ? s[nt][e] * scale : -INFINITY;
-        mx[rs] = fmaxf(mx[rs], s[nt][e]);
-      }
+        for (int e = 0; e < 4; ++e) {
+          s[nt][e] *= scale;
+          mx[e >> 1] = fmaxf(mx[e >> 1], s[nt][e]);
+        }
+    } else {
+#pragma unroll
+      for (int nt = 0; nt < MK / 8; ++nt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int j = kpos[nt * 8 + 2 * tq + (e & 1)], rs = e >> 1, p = p_row[rs];
+          const bool ok = j >= 0 && row_ok[rs] && j <= p && (window == 0 || p - j < window || j < keep_first);
+          s[nt][e] = ok ? s[nt][e] * scale : -INFINITY;
+          mx[rs] = fmaxf(mx[rs], s[nt][e]);
+        }
+    }
     float alpha[2];
 #pragma unroll
     for (int rs = 0; rs < 2; ++rs) {
       mx[rs] = fmaxf(mx[rs], __shfl_xor_sync(0xffffffffu, mx[rs], 1));
       mx[rs] = fmaxf(mx[rs], __shfl_xor_sync(0xffffffffu, mx[rs], 2));
       const float m_new = fmaxf(m_r[rs], mx[rs]);
-      alpha[rs] = m_new > -INFINITY ? expf(m_r[rs] - m_new) : 1.f;      // 0 while m_r is still -inf
+      alpha[rs] = m_new > -INFINITY ? __expf(m_r[rs] - m_new) : 1.f;    // 0 while m_r is still -inf
       m_r[rs] = m_new;
     }
     float sum[2] = {0.f, 0.f};
@@ -441,7 +472,7 @@ sink_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const int rs = e >> 1;
-        const float pv = s[nt][e] > -INFINITY ? expf(s[nt][e] - m_r[rs]) : 0.f;
+        const float pv = s[nt][e] > -INFINITY ? __expf(s[nt][e] - m_r[rs]) : 0.f;     // bfloat16 follows: the fast form will do
         s[nt][e] = pv;
         sum[rs] += pv;
       }
@@ -470,7 +501,7 @@ sink_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat
           mma16816(o[2 * vp + 1], a, b2, b3);
         }
     }
-    __syncthreads();        // the tiles are overwritten by the next round
+    __syncthreads();        // this stage is refilled in the next round
   }
 
 #pragma unroll
@@ -569,8 +600,14 @@ extern "C" int flint_sink_attention_tiles(const void* q, const void* k_cache, co
   if (nkv <= 0 || nq % nkv) return fail("sink_attention_tiles: %d query heads do not divide into %d kv heads", nq, nkv);
   if (window < 0 || keep_first < 0 || page_size <= 0) return fail("sink_attention_tiles: bad window or page size");
   if ((long long)n_tiles * nq > 0x7fffffffLL) return fail("sink_attention_tiles: too many work items");
-  const size_t smem = (size_t)MK * ((hd + 8) + (vd + 8)) * 2 + MK * sizeof(int);
+  const size_t smem = 2 * ((size_t)MK * ((hd + 8) + (vd + 8)) * 2 + MK * sizeof(int));       // two stages
   const dim3 grid((unsigned)(n_tiles * nq)), block(128);
+  static bool sized = false;
+  if (!sized) {             // the larger form's two stages exceed the default limit of dynamic shared memory
+    cudaFuncSetAttribute(sink_attention_mma_kernel<4, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+    cudaFuncSetAttribute(sink_attention_mma_kernel<8, 16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+    sized = true;
+  }
   const __nv_bfloat16 *qq = (const __nv_bfloat16*)q, *kk = (const __nv_bfloat16*)k_cache, *vv = (const __nv_bfloat16*)v_cache;
   if (hd <= 64 && vd <= 64)
     launch_pdl(sink_attention_mma_kernel<4, 8>, grid, block, smem, stream, qq, kk, vv, block_table, max_pages, page_size, tiles,
