@@ -299,6 +299,7 @@ __global__ void sink_combine_kernel(const float* __restrict__ scratch, TO* __res
 // softmax in float32 on the accumulator fragment, P as bfloat16 the A operand of O += P V with V through ldmatrix.trans.
 // The sink joins maximum and sum at the end.
 constexpr int MQ = 64, MK = 64;      // query rows a block, keys a tile
+static_assert(MK * 2 == 128, "two of the block's 128 threads fetch a key");
 
 __device__ __forceinline__ void ldsm4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
@@ -386,20 +387,21 @@ sink_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat
       const int u = u0 + r;
       return u < total ? (u < n_first ? u : base + (u - n_first)) : -1;
     };
-    if (tid < MK) pos_d[tid] = key_at(tid);
-    for (int i = tid; i < MK * chunks_k; i += 128) {
-      const int r = i / chunks_k, c = i % chunks_k, j = key_at(r);
-      const int page = j >= 0 ? bt[j / page_size] : -1;
-      __nv_bfloat16* dst = k_d + r * ldk + c * 8;
-      if (page >= 0) copy16(dst, k_cache + (((size_t)page * nkv + kvh) * page_size + j % page_size) * hd + c * 8);
-      else *reinterpret_cast<uint4*>(dst) = make_uint4(0u, 0u, 0u, 0u);
-    }
-    for (int i = tid; i < MK * chunks_v; i += 128) {
-      const int r = i / chunks_v, c = i % chunks_v, j = key_at(r);
-      const int page = j >= 0 ? bt[j / page_size] : -1;
-      __nv_bfloat16* dst = v_d + r * ldv + c * 8;
-      if (page >= 0) copy16(dst, v_cache + (((size_t)page * nkv + kvh) * page_size + j % page_size) * vd + c * 8);
-      else *reinterpret_cast<uint4*>(dst) = make_uint4(0u, 0u, 0u, 0u);
+    // two threads a key: the key's position and page are worked out once, then the row's 16-byte pieces alternate
+    const int r = tid >> 1, half = tid & 1, j = key_at(r);
+    if (half == 0) pos_d[r] = j;
+    const int page = j >= 0 ? bt[j / page_size] : -1;
+    __nv_bfloat16* kd = k_d + r * ldk;
+    __nv_bfloat16* vd_ = v_d + r * ldv;
+    if (page >= 0) {
+      const size_t at = ((size_t)page * nkv + kvh) * page_size + j % page_size;
+      const __nv_bfloat16* ks = k_cache + at * hd;
+      const __nv_bfloat16* vs = v_cache + at * vd;
+      for (int c = half; c < chunks_k; c += 2) copy16(kd + c * 8, ks + c * 8);
+      for (int c = half; c < chunks_v; c += 2) copy16(vd_ + c * 8, vs + c * 8);
+    } else {
+      for (int c = half; c < chunks_k; c += 2) *reinterpret_cast<uint4*>(kd + c * 8) = make_uint4(0u, 0u, 0u, 0u);
+      for (int c = half; c < chunks_v; c += 2) *reinterpret_cast<uint4*>(vd_ + c * 8) = make_uint4(0u, 0u, 0u, 0u);
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
   };
