@@ -7,8 +7,8 @@
 // Three kernels.  flint_mlstm_prepare adds up the partial sums of the input projection [q | k | v | g | z_i | z_f]
 // and turns them into what the recurrence reads: q times D^(-1/2), i = cap tanh((z_i + b_i) / cap),
 // f = logsigmoid(cap tanh((z_f + b_f) / cap)); it is parallel over tokens.  flint_mlstm_scan walks the tokens of
-// every request in order, in two kernels: one warp per (request, head) carries m and n and leaves every token's
-// decay, intake and denominator; then a warp per CW columns of one head's S (lane l holds rows l, l + 32, ... of
+// every request in order, in two kernels: one block per (request, head), a thread per dim of n, carries m and n and
+// leaves every token's decay, intake and denominator; then a warp per CW columns of one head's S (lane l holds rows l, l + 32, ... of
 // each) carries those columns, so no warp touches another's part of the state; a block stages the operands of eight
 // tokens at a time in shared memory by asynchronous copies, two stages alternating, so the walk does not wait
 // for global memory.  The state is read from and written back to the request's row of the state slab
